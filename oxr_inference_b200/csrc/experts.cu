@@ -4,6 +4,9 @@
 // neighbours; a group's score is the sum of its two largest s (of its only one, when groups hold one expert); only experts
 // of the `keep` best groups can be chosen. The `top` allowed experts with the largest s are chosen (the lower index wins a
 // tie); their weights are their s divided by the sum of the chosen s (+ 1e-20), times `scale`. All of it in fp32.
+// Variants, each an argument: scores that are the softmax of z over all experts instead of sigmoids (score_kind 1); a group's
+// score that is its largest s instead of the sum of its two largest (group_kind 1); weights that are the chosen s themselves,
+// times `scale`, not divided by their sum (renorm 0).
 //
 // For steps of many tokens the experts run one after the other instead, each over the tokens that chose it (`expert_sort`, `gather_rows`,
 // then per expert two products and the activation, then `combine_rows`): the work is then that of the chosen experts only.
@@ -18,12 +21,19 @@ constexpr int ROUTE_MAX_TOP = 32;
 constexpr int ROUTE_MAX_GROUPS = 64;
 
 __global__ void route_kernel(float* __restrict__ gate, int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ z, int n_tokens,
-                             int E, int top, int groups, int keep, float scale) {
+                             int E, int top, int groups, int keep, float scale, int score_kind, int group_kind, int renorm) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n_tokens) return;
     float* row = gate + (size_t)t * E;          // scratch for the scores until the last pass
     const float* zr = z + (size_t)t * E;
-    for (int e = 0; e < E; ++e) row[e] = 1.f / (1.f + expf(-zr[e]));
+    if (score_kind == 1) {
+        float zmax = -INFINITY, den = 0.f;
+        for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, zr[e]);
+        for (int e = 0; e < E; ++e) { row[e] = expf(zr[e] - zmax); den += row[e]; }
+        for (int e = 0; e < E; ++e) row[e] = row[e] / den;
+    } else {
+        for (int e = 0; e < E; ++e) row[e] = 1.f / (1.f + expf(-zr[e]));
+    }
     unsigned long long allowed = ~0ull;        // one bit per group
     const int per = E / groups;
     if (groups > 1 && keep < groups) {
@@ -35,7 +45,7 @@ __global__ void route_kernel(float* __restrict__ gate, int* __restrict__ ids, fl
                 if (v > a) { b = a; a = v; }
                 else if (v > b) b = v;
             }
-            score[g] = a + (b >= 0.f ? b : 0.f);
+            score[g] = group_kind == 1 ? a : a + (b >= 0.f ? b : 0.f);
         }
         allowed = 0ull;
         for (int i = 0; i < keep; ++i) {
@@ -60,7 +70,7 @@ __global__ void route_kernel(float* __restrict__ gate, int* __restrict__ ids, fl
         chosen_s[i] = best >= 0 ? best_v : 0.f;
         if (best >= 0) { row[best] = -1.f; sum += best_v; }
     }
-    const float norm = scale / (sum + 1e-20f);
+    const float norm = renorm ? scale / (sum + 1e-20f) : scale;
     for (int e = 0; e < E; ++e) row[e] = 0.f;
     for (int i = 0; i < top; ++i) {
         const float w = chosen_s[i] * norm;
@@ -86,14 +96,24 @@ __device__ __forceinline__ void warp_argmax(float& v, int& idx) {
 }
 
 __global__ void __launch_bounds__(128) route_warp_kernel(float* __restrict__ gate, int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ z,
-                                                        int n_tokens, int E, int top, int groups, int keep, float scale) {
+                                                        int n_tokens, int E, int top, int groups, int keep, float scale, int score_kind,
+                                                        int group_kind, int renorm) {
     __shared__ float sc[4][ROUTE_WARP_MAX_E];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 4 + warp;
     if (t >= n_tokens) return;
     float* s = sc[warp];
     const int per = E / groups;
-    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[(size_t)t * E + e]));
+    if (score_kind == 1) {
+        float zmax = -INFINITY, den = 0.f;
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[(size_t)t * E + e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < E; e += 32) { s[e] = expf(z[(size_t)t * E + e] - zmax); den += s[e]; }
+        den = warp_sum(den);
+        for (int e = lane; e < E; e += 32) s[e] = s[e] / den;
+    } else {
+        for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[(size_t)t * E + e]));
+    }
     __syncwarp();
     unsigned allowed = 0xffffffffu;            // one bit per group
     if (groups > 1 && keep < groups) {
@@ -105,7 +125,7 @@ __global__ void __launch_bounds__(128) route_warp_kernel(float* __restrict__ gat
                 if (v > a) { b = a; a = v; }
                 else if (v > b) b = v;
             }
-            score = a + (b >= 0.f ? b : 0.f);
+            score = group_kind == 1 ? a : a + (b >= 0.f ? b : 0.f);
         }
         allowed = 0u;
         for (int i = 0; i < keep; ++i) {
@@ -131,7 +151,7 @@ __global__ void __launch_bounds__(128) route_warp_kernel(float* __restrict__ gat
         sum += v;
         __syncwarp();
     }
-    const float norm = scale / (sum + 1e-20f);
+    const float norm = renorm ? scale / (sum + 1e-20f) : scale;
     for (int e = lane; e < E; e += 32) gate[(size_t)t * E + e] = 0.f;
     __syncwarp();
     if (lane < top) {
@@ -143,15 +163,15 @@ __global__ void __launch_bounds__(128) route_warp_kernel(float* __restrict__ gat
 }
 
 OXR_API int oxr_route(float* gate, int* ids, float* wts, const float* z, int n_tokens, int E, int top, int groups, int keep, float scale,
-                      cudaStream_t stream) {
+                      int score_kind, int group_kind, int renorm, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || groups <= 0 || groups > ROUTE_MAX_GROUPS || E % groups || keep <= 0 || keep > groups ||
-        top > keep * (E / groups))
+        top > keep * (E / groups) || score_kind < 0 || score_kind > 1 || group_kind < 0 || group_kind > 1)
         return OXR_BAD_ARGUMENT;
     if (E <= ROUTE_WARP_MAX_E && groups <= 32)
-        route_warp_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale);
+        route_warp_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale, score_kind, group_kind, renorm);
     else
-        route_kernel<<<(n_tokens + 63) / 64, 64, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale);
+        route_kernel<<<(n_tokens + 63) / 64, 64, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale, score_kind, group_kind, renorm);
     return oxr_launch_status();
 }
 
@@ -199,6 +219,34 @@ OXR_API int oxr_gated_relu2(void* a, const void* u, const float* gate, int n_tok
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0) gated_relu2_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)u, gate, total, E * ff, ff, E);
     else gated_relu2_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)u, gate, total, E * ff, ff, E);
+    return oxr_launch_status();
+}
+
+// The clamped gated unit over the stacked columns of all experts: gu[t] = E stretches [gate (ff) | up (ff)], one per expert;
+// a[t, e ff + c] = gate_w[t, e] * g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate_w None: 1.
+template <typename T>
+__global__ void expert_clamped_glu_kernel(T* __restrict__ a, const T* __restrict__ gu, const float* __restrict__ gate_w, size_t total, int ff, int E,
+                                          float alpha, float limit) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cols = E * ff;
+    const size_t t = i / cols;
+    const int c = (int)(i - t * cols), e = c / ff, k = c - e * ff;
+    const float w = gate_w != nullptr ? gate_w[t * E + e] : 1.f;
+    const T* src = gu + t * 2 * cols + (size_t)e * 2 * ff;
+    const float g = fminf(Num<T>::to_f32(src[k]), limit);
+    const float u = fminf(fmaxf(Num<T>::to_f32(src[ff + k]), -limit), limit);
+    a[i] = Num<T>::from_f32(w * (g / (1.f + expf(-alpha * g)) * (u + 1.f)));
+}
+
+OXR_API int oxr_expert_clamped_glu(void* a, const void* gu, const float* gate_w, int n_tokens, int E, int ff, float alpha, float limit, int dtype,
+                                   cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (E <= 0 || ff <= 0) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n_tokens * E * ff;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) expert_clamped_glu_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)gu, gate_w, total, ff, E, alpha, limit);
+    else expert_clamped_glu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)gu, gate_w, total, ff, E, alpha, limit);
     return oxr_launch_status();
 }
 

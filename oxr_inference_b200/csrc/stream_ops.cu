@@ -273,3 +273,141 @@ OXR_API int oxr_rotary_angles(float* cos_out, float* sin_out, const int* positio
     rotary_angles_kernel<<<(total + 127) / 128, 128, 0, stream_>>>(cos_out, sin_out, positions, freq, half, total);
     return oxr_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------- layer norm of the stream
+// out[r] = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight + bias for stream row `rows ? rows[r] : r`; the mean first,
+// then the mean of the squared deviations (two passes, not E[x^2] - E[x]^2), all in fp32. One block per output row.
+template <typename T>
+__global__ void stream_layer_norm_kernel(T* __restrict__ out, const float* __restrict__ stream, const float* __restrict__ weight,
+                                         const float* __restrict__ bias, const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* x = stream + (size_t)(rows ? rows[r] : r) * hidden;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) s += x[i];
+    const float mean = block_sum(s, red) / (float)hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = x[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    T* dst = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float b = bias != nullptr ? bias[i] : 0.f;
+        dst[i] = Num<T>::from_f32((x[i] - mean) * inv * weight[i] + b);
+    }
+}
+
+OXR_API int oxr_stream_layer_norm(void* out, const float* stream, const float* weight, const float* bias, const int* rows, int n_out, int hidden,
+                                  float eps, int dtype, cudaStream_t stream_) {
+    if (n_out <= 0) return 0;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == 0) stream_layer_norm_kernel<float><<<n_out, threads, 0, stream_>>>((float*)out, stream, weight, bias, rows, hidden, eps);
+    else stream_layer_norm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream_>>>((__nv_bfloat16*)out, stream, weight, bias, rows, hidden, eps);
+    return oxr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------- gated residual, depth average
+// What a block with side-by-side sublayers does to the fp32 stream once both sublayers are done, in one pass:
+//
+//   X = stream + ( a * sigmoid(ga + ba) + f * sigmoid(gf + bf) )          the gates (ga, gf: columns 0.. and hidden.. of `gates`, with
+//                                                                        fp32 biases) are optional, and so is the second sublayer f;
+//   history[index] = X                                                   when a history [slots, tokens, hidden] is kept, and then
+//   stream = sum_{j < index} mixw[j] * history[j] + mixw[index] * X       (the sum in the order of j), else stream = X.
+//
+// ab / fb: an optional fp32 bias row added to a / f before anything else (a sublayer's output bias).
+template <typename T>
+__global__ void gated_residual_kernel(float* __restrict__ stream, const T* __restrict__ a, const float* __restrict__ ab, const T* __restrict__ f,
+                                      const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride, const float* __restrict__ gate_bias,
+                                      float* __restrict__ history, int index, const float* __restrict__ mixw, int hidden, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / hidden;
+        const int c = (int)(i - row * hidden);
+        float y = Num<T>::to_f32(a[i]);
+        if (ab != nullptr) y += ab[c];
+        if (gates != nullptr) {
+            const float g = Num<T>::to_f32(gates[row * gates_stride + c]) + (gate_bias != nullptr ? gate_bias[c] : 0.f);
+            y = y / (1.f + expf(-g));
+        }
+        if (f != nullptr) {
+            float z = Num<T>::to_f32(f[i]);
+            if (fb != nullptr) z += fb[c];
+            if (gates != nullptr) {
+                const float g = Num<T>::to_f32(gates[row * gates_stride + hidden + c]) + (gate_bias != nullptr ? gate_bias[hidden + c] : 0.f);
+                z = z / (1.f + expf(-g));
+            }
+            y += z;
+        }
+        float x = stream[i] + y;
+        if (history != nullptr) {
+            history[(size_t)index * total + i] = x;
+            float acc = 0.f;
+            for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
+            x = fmaf(mixw[index], x, acc);
+        }
+        stream[i] = x;
+    }
+}
+
+OXR_API int oxr_gated_residual(float* stream, const void* a, const float* ab, const void* f, const float* fb, const void* gates, int gates_stride,
+                               const float* gate_bias, float* history, int index, const float* mixw, int n, int hidden, int dtype,
+                               cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    if (hidden <= 0 || a == nullptr || (history != nullptr && (mixw == nullptr || index < 0))) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n * hidden;
+    if (dtype == 0)
+        gated_residual_kernel<float><<<grid_for(total, 256), 256, 0, stream_>>>(stream, (const float*)a, ab, (const float*)f, fb, (const float*)gates,
+                                                                               gates_stride, gate_bias, history, index, mixw, hidden, total);
+    else
+        gated_residual_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream_>>>(stream, (const __nv_bfloat16*)a, ab, (const __nv_bfloat16*)f, fb,
+                                                                                       (const __nv_bfloat16*)gates, gates_stride, gate_bias, history,
+                                                                                       index, mixw, hidden, total);
+    return oxr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------- tanh GELU
+// out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), fp32 arithmetic, rounded once; out may be x itself.
+template <typename T>
+__global__ void gelu_tanh_kernel(T* __restrict__ out, const T* __restrict__ x, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = Num<T>::to_f32(x[i]);
+        out[i] = Num<T>::from_f32(0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+    }
+}
+
+__global__ void gelu_tanh_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ x, size_t total8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+        float z[8], o[8];
+        bf16x8_to_f32(x[i], z);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = 0.5f * z[k] * (1.f + tanhf(0.7978845608028654f * (z[k] + 0.044715f * z[k] * z[k] * z[k])));
+        out[i] = f32_to_bf16x8(o);
+    }
+}
+
+OXR_API int oxr_gelu_tanh(void* out, const void* x, long long total, int dtype, cudaStream_t stream_) {
+    if (total <= 0) return 0;
+    if (dtype == 1 && total % 8 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)x % 16 == 0) {
+        gelu_tanh_bf16x8_kernel<<<grid_for((size_t)total / 8, 256), 256, 0, stream_>>>((uint4*)out, (const uint4*)x, (size_t)total / 8);
+        return oxr_launch_status();
+    }
+    if (dtype == 0) gelu_tanh_kernel<float><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((float*)out, (const float*)x, (size_t)total);
+    else gelu_tanh_kernel<__nv_bfloat16><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (size_t)total);
+    return oxr_launch_status();
+}
+
+// y += x element by element (the sum in fp32, rounded once)
+template <typename T>
+__global__ void add_inplace_kernel(T* __restrict__ y, const T* __restrict__ x, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = Num<T>::from_f32(Num<T>::to_f32(y[i]) + Num<T>::to_f32(x[i]));
+}
+
+OXR_API int oxr_add_inplace(void* y, const void* x, long long total, int dtype, cudaStream_t stream_) {
+    if (total <= 0) return 0;
+    if (dtype == 0) add_inplace_kernel<float><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((float*)y, (const float*)x, (size_t)total);
+    else add_inplace_kernel<__nv_bfloat16><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, (size_t)total);
+    return oxr_launch_status();
+}

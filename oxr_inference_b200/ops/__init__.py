@@ -143,12 +143,23 @@ def _lib():
         lib.oxr_scale_f32.argtypes = [p, f, ll, p]
         lib.oxr_mlstm_scan.argtypes = [p, p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
         lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
-        lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, p]
+        lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, i, i, i, p]
         lib.oxr_gated_relu2.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_expert_sort.argtypes = [p, p, p, p, p, i, i, i, i, p]
         lib.oxr_gemm_tcgen05_grouped_bf16.argtypes = [p, p, p, i, i, i, i, p, i, i, i, p, p]
         lib.oxr_gather_rows.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_combine_rows.argtypes = [p, p, p, p, i, i, i, i, p]
+        lib.oxr_stream_layer_norm.argtypes = [p, p, p, p, p, i, i, f, i, p]
+        lib.oxr_gated_residual.argtypes = [p, p, p, p, p, p, i, p, p, i, p, i, i, i, p]
+        lib.oxr_gelu_tanh.argtypes = [p, p, ll, i, p]
+        lib.oxr_add_inplace.argtypes = [p, p, ll, i, p]
+        lib.oxr_add_inplace.restype = c_int
+        lib.oxr_attention_mix_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, f, p, i, i, p, i, i, p, p]
+        lib.oxr_bias_rope_store.argtypes = [p, i, i, i, i, i, p, p, p, i, p, p, ll, p, i, i, p, p]
+        lib.oxr_expert_clamped_glu.argtypes = [p, p, p, i, i, i, f, f, i, p]
+        for name in ("oxr_stream_layer_norm", "oxr_gated_residual", "oxr_gelu_tanh", "oxr_attention_mix_rows", "oxr_bias_rope_store",
+                     "oxr_expert_clamped_glu"):
+            getattr(lib, name).restype = c_int
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
                      "oxr_mamba_conv", "oxr_mamba_scan", "oxr_gated_group_norm", "oxr_attention_rows", "oxr_scatter_rows", "oxr_latent_prep",
                      "oxr_head_linear", "oxr_conv_qkv_store", "oxr_add_bias", "oxr_scale_f32", "oxr_mlstm_scan", "oxr_head_norm_gate", "oxr_route",
@@ -1108,6 +1119,133 @@ def rotary_angles(positions: torch.Tensor, freq: torch.Tensor) -> tuple[torch.Te
     return cos, sin
 
 
+def stream_layer_norm(stream: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
+                      rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``(x - mean) / sqrt(mean((x - mean)^2) + eps) * weight + bias`` of an fp32 stream ``[tokens, hidden]``, rounded to ``out_dtype``; with
+    ``rows`` (int32) only those rows."""
+    _need(stream, "stream", torch.float32)
+    _need(weight, "weight", torch.float32)
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    n, hidden = stream.shape
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    out = torch.empty((n, hidden), dtype=out_dtype, device=stream.device)
+    _done(_lib().oxr_stream_layer_norm(out.data_ptr(), stream.data_ptr(), weight.data_ptr(), _ptr(bias), _ptr(rows), n, hidden, float(eps),
+                                       _DT[out_dtype], _stream()), "stream_layer_norm")
+    return out
+
+
+def gated_residual(stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None = None, *, gates: torch.Tensor | None = None,
+                   gate_bias: torch.Tensor | None = None, a_bias: torch.Tensor | None = None, f_bias: torch.Tensor | None = None,
+                   history: torch.Tensor | None = None, index: int = 0, weights: torch.Tensor | None = None) -> torch.Tensor:
+    """In place on the fp32 stream: ``X = stream + (a' + f')`` where ``a' = (a + a_bias) * sigmoid(gates[:, :hidden] + gate_bias[:hidden])`` and
+    ``f'`` likewise with the second half of ``gates`` (no gates: the sublayers' outputs as they are; ``f`` None: one sublayer). With a
+    ``history [slots, tokens, hidden]`` (fp32) X is kept as ``history[index]`` and the stream becomes ``sum_{j <= index} weights[j] history[j]``."""
+    _need(stream, "stream", torch.float32)
+    _need(a, "a")
+    n, hidden = stream.shape
+    if a.shape != stream.shape or (f is not None and (f.shape != stream.shape or f.dtype != a.dtype)):
+        raise KernelError("gated_residual: the sublayers' outputs do not match the stream")
+    stride = 0
+    if gates is not None:
+        _need(gates, "gates", a.dtype)
+        stride = gates.shape[1]
+        if gates.shape[0] != n or stride < (2 if f is not None else 1) * hidden:
+            raise KernelError("gated_residual: the gates do not fit")
+    for t, name in ((gate_bias, "gate_bias"), (a_bias, "a_bias"), (f_bias, "f_bias")):
+        if t is not None:
+            _need(t, name, torch.float32)
+    if history is not None:
+        _need(history, "history", torch.float32)
+        _need(weights, "weights", torch.float32)
+        if history.shape[1:] != stream.shape or not 0 <= index < history.shape[0] or weights.numel() <= index:
+            raise KernelError("gated_residual: the history does not fit")
+    _done(_lib().oxr_gated_residual(stream.data_ptr(), a.data_ptr(), _ptr(a_bias), _ptr(f), _ptr(f_bias), _ptr(gates), stride, _ptr(gate_bias),
+                                    _ptr(history), int(index), _ptr(weights), n, hidden, _dtype_code(a), _stream()), "gated_residual")
+    return stream
+
+
+def gelu_tanh_(x: torch.Tensor) -> torch.Tensor:
+    """In place ``0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))``, fp32 arithmetic."""
+    _need(x, "x")
+    _done(_lib().oxr_gelu_tanh(x.data_ptr(), x.data_ptr(), x.numel(), _dtype_code(x), _stream()), "gelu_tanh")
+    return x
+
+
+def add_(y: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """In place ``y += x`` (tensors of one shape and type; the sum in fp32, rounded once)."""
+    _need(y, "y")
+    _need(x, "x", y.dtype)
+    if x.shape != y.shape:
+        raise KernelError("add_: shapes differ")
+    _done(_lib().oxr_add_inplace(y.data_ptr(), x.data_ptr(), y.numel(), _dtype_code(y), _stream()), "add_")
+    return y
+
+
+def bias_rope_store(proj: torch.Tensor, cq: int, ck: int, cv: int, key_dim: int, *, bias: torch.Tensor | None, cos: torch.Tensor | None,
+                    sin: torch.Tensor | None, k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor, status: torch.Tensor) -> None:
+    """Between a stacked ``[q | k | v | ...]`` product and attention: every entry of q, k and v gets its ``bias`` (fp32 ``[cq + ck + cv]``), entry
+    pairs (2i, 2i+1) of the first ``2 * cos.shape[1]`` entries of every q and k head turn by the token's angles (``cos`` / ``sin``
+    ``[tokens, pairs]``), q goes back in place, k and v go to their pools at ``slots`` (slot -1: not stored)."""
+    _need(proj, "proj")
+    _need(k_pool, "k_pool", proj.dtype)
+    _need(v_pool, "v_pool", proj.dtype)
+    n = proj.shape[0]
+    half = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32)
+        _need(sin, "sin", torch.float32)
+        half = cos.shape[1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != cq + ck + cv:
+            raise KernelError("bias_rope_store: the bias does not fit")
+    if k_pool[0, 0].numel() != ck or v_pool[0, 0].numel() != cv or k_pool.shape[:2] != v_pool.shape[:2]:
+        raise KernelError("bias_rope_store: the pools do not fit the projections")
+    _done(_lib().oxr_bias_rope_store(proj.data_ptr(), proj.shape[1], int(cq), int(ck), int(cv), int(key_dim), _ptr(bias), _ptr(cos), _ptr(sin), half,
+                                     k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0] * k_pool.shape[1], slots.data_ptr(), n, _dtype_code(proj),
+                                     status.data_ptr(), _stream()), "bias_rope_store")
+
+
+def attention_mix_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, *, positions: torch.Tensor,
+                       req_of_token: torch.Tensor, block_table: torch.Tensor, scale: float, softcap: float = 0.0,
+                       head_mix: torch.Tensor | None = None, unit_sink: bool = False, window: int = 0, gate: torch.Tensor | None = None,
+                       status: torch.Tensor) -> torch.Tensor:
+    """Attention of the step's tokens over the paged cache in which the heads' scores are mixed before the softmax, in fp32 arithmetic.
+
+    ``q [tokens, >= H * DK]`` (the queries are the first columns, so a stacked product can be handed over); ``k_pool [pages, page_size, KV, DK]``,
+    ``v_pool [pages, page_size, KV, DV]``. Token t at position p sees keys j <= p (the last ``window`` only, when given). The scaled score is
+    capped as ``softcap * tanh(s / softcap)`` (0: no cap), then ``head_mix [H, H]`` (fp32) makes head h's score ``sum_g head_mix[h, g] s_g``;
+    ``unit_sink`` adds one to the softmax denominator; ``gate`` (a view ``[tokens, H * DV]`` whose rows may be strided) multiplies the output by
+    its sigmoid. Returns ``[tokens, H * DV]``."""
+    _need(q, "q")
+    _need(k_pool, "k_pool", q.dtype)
+    _need(v_pool, "v_pool", q.dtype)
+    n, H = q.shape[0], int(num_heads)
+    pages, page_size, KV, DK = k_pool.shape
+    DV = v_pool.shape[3]
+    if q.dim() != 2 or q.shape[1] < H * DK or v_pool.shape[:3] != k_pool.shape[:3]:
+        raise KernelError("attention_mix_rows: sizes do not fit")
+    if head_mix is not None:
+        _need(head_mix, "head_mix", torch.float32)
+        if head_mix.shape != (H, H):
+            raise KernelError("attention_mix_rows: the mixing matrix must be [heads, heads]")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.shape != (n, H * DV) or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("attention_mix_rows: the gate does not fit")
+        gate_stride = gate.stride(0)
+    out = torch.empty((n, H * DV), dtype=q.dtype, device=q.device)
+    _done(_lib().oxr_attention_mix_rows(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), KV * DK, DK, v_pool.data_ptr(), KV * DV, DV, DK, DV, H,
+                                        KV, n, positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size,
+                                        pages, float(scale), float(softcap), _ptr(head_mix), int(bool(unit_sink)), int(window),
+                                        gate.data_ptr() if gate is not None else None, gate_stride, _dtype_code(q), status.data_ptr(), _stream()),
+          "attention_mix_rows")
+    return out
+
+
 # --------------------------------------------------------------------------------------------------- Mamba-2
 def mamba_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, tail: torch.Tensor, *, req_of_token: torch.Tensor,
                cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int) -> torch.Tensor:
@@ -1374,19 +1512,44 @@ def head_norm_gate(y: torch.Tensor, proj: torch.Tensor, gate_col0: int, weight: 
 
 
 # --------------------------------------------------------------------------------------------------- routed experts
-def route(z: torch.Tensor, *, top: int, groups: int, keep: int, scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Router logits ``z [tokens, E]`` (fp32) to the choice of ``top`` experts per token: scores are ``sigmoid(z)``; of ``groups`` equal groups of
-    neighbouring experts only the ``keep`` with the largest sum of their two best scores may be chosen from; the weights are the chosen scores
-    over their sum, times ``scale``. Returns ``gate [tokens, E]`` (fp32: a chosen expert's weight, else 0), ``ids [tokens, top]`` (int32) and
-    ``weights [tokens, top]`` (fp32)."""
+ROUTE_SCORES = {"sigmoid": 0, "softmax": 1}
+ROUTE_GROUP_SCORES = {"top2_sum": 0, "max": 1}
+
+
+def route(z: torch.Tensor, *, top: int, groups: int, keep: int, scale: float, score: str = "sigmoid", group_score: str = "top2_sum",
+          renormalize: bool = True) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Router logits ``z [tokens, E]`` (fp32) to the choice of ``top`` experts per token. Scores are ``sigmoid(z)`` or, with ``score="softmax"``,
+    the softmax of z over all experts; of ``groups`` equal groups of neighbouring experts only the ``keep`` best may be chosen from, a group's
+    score being the sum of its two best scores (``"top2_sum"``) or its best score (``"max"``); the weights are the chosen scores over their sum
+    (``renormalize``) or as they are, times ``scale``. Returns ``gate [tokens, E]`` (fp32: a chosen expert's weight, else 0), ``ids [tokens, top]``
+    (int32) and ``weights [tokens, top]`` (fp32)."""
     _need(z, "z", torch.float32)
     n, E = z.shape
     gate = torch.empty((n, E), dtype=torch.float32, device=z.device)
     ids = torch.empty((n, top), dtype=torch.int32, device=z.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=z.device)
-    _done(_lib().oxr_route(gate.data_ptr(), ids.data_ptr(), wts.data_ptr(), z.data_ptr(), n, E, int(top), int(groups), int(keep), float(scale), _stream()),
-          "route")
+    _done(_lib().oxr_route(gate.data_ptr(), ids.data_ptr(), wts.data_ptr(), z.data_ptr(), n, E, int(top), int(groups), int(keep), float(scale),
+                           ROUTE_SCORES[score], ROUTE_GROUP_SCORES[group_score], int(bool(renormalize)), _stream()), "route")
     return gate, ids, wts
+
+
+def expert_clamped_glu(gu: torch.Tensor, gate: torch.Tensor | None, ff: int, *, alpha: float, limit: float) -> torch.Tensor:
+    """The clamped gated unit over the stacked gate and up projections of all experts: ``gu [tokens, E * 2 ff]`` holds, expert by expert,
+    ``[gate (ff) | up (ff)]``; ``a[t, e ff + c] = gate[t, e] * g sigmoid(alpha g) (u + 1)`` with ``g = min(gate_c, limit)`` and
+    ``u = clamp(up_c, -limit, limit)``; ``gate`` None: no weight (one expert's rows)."""
+    _need(gu, "gu")
+    n, cols2 = gu.shape
+    E = cols2 // (2 * ff)
+    if cols2 != E * 2 * ff or E < 1:
+        raise KernelError("expert_clamped_glu: sizes do not fit")
+    if gate is not None:
+        _need(gate, "gate", torch.float32)
+        if gate.shape != (n, E):
+            raise KernelError("expert_clamped_glu: sizes do not fit")
+    a = torch.empty((n, E * ff), dtype=gu.dtype, device=gu.device)
+    _done(_lib().oxr_expert_clamped_glu(a.data_ptr(), gu.data_ptr(), _ptr(gate), n, E, int(ff), float(alpha), float(limit), _dtype_code(gu), _stream()),
+          "expert_clamped_glu")
+    return a
 
 
 def gated_relu2(u: torch.Tensor, gate: torch.Tensor | None, ff: int, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -4,7 +4,9 @@ from __future__ import annotations
 
 import torch
 
-from oxr_inference_b200.parts.base import ARRANGEMENTS, DeferredLinear, FeedForward, LayerCache, Mixer, Norm, StepContext
+from oxr_inference_b200 import ops
+from oxr_inference_b200.parts.base import ARRANGEMENTS, DeferredLinear, FeedForward, LayerCache, Mixer, Norm, ParamInfo, Part, Runtime, StepContext
+from oxr_inference_b200.parts.linear import StackedLinear
 
 
 @ARRANGEMENTS.register("pre_norm")
@@ -107,4 +109,104 @@ class SandwichNormBlock:
             return None, stream
         h = self.mixer_post_norm.add_normed(stream, a, then=self.feed_forward_norm)
         self.feed_forward_post_norm.add_normed(stream, self.feed_forward.forward(h))
+        return None, stream
+
+
+@ARRANGEMENTS.register("parallel")
+class ParallelBlock(Part):
+    """``x <- x + (mixer(h) + feed_forward(h))`` with ONE norm, ``h = norm(x)``, that both sublayers read (the feed-forward may be absent).
+    Two options, each with tensors of the block's own:
+
+    * ``gated``: each sublayer's result is multiplied element by element by ``sigmoid(W h + b)`` before it is added: ``rg1`` / ``rg1.b`` for
+      the mixer, ``rg2`` / ``rg2.b`` for the feed-forward (both maps are one product);
+    * ``depth_states`` = d > 0: the block keeps its result X as state d - 1 of the step's history (state 0 is the embedding's output, put
+      there by the first such block; ``history_slots`` says how many states the model has) and hands on ``sum_{j < d} dwa[j] X_j``
+      instead of X. The history lives in the step's shared dictionary under ``history_key``.
+
+    The stream is kept whole in fp32, as in ``sandwich_norm``: ``forward`` takes it in ``residual`` (the first block: in ``x``), updates it
+    in place and returns ``(None, stream)``. Gates, both adds, the history entry and the weighted sum are one kernel."""
+
+    supports_deferred = False
+    accepts_deferred_input = False
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward | None, feed_forward_norm: Norm | None, *, runtime: Runtime,
+                 hidden_size: int, gated: bool = False, depth_states: int = 0, history_slots: int = 0, history_key: str = "depth_history"):
+        if feed_forward_norm is not None:
+            raise ValueError("the parallel arrangement has one norm: its feed-forward reads the mixer's")
+        if depth_states and not 2 <= depth_states <= history_slots:
+            raise ValueError(f"a block that averages {depth_states} states needs at least 2 and a history of at least as many slots ({history_slots})")
+        if not hasattr(mixer_norm, "stream_norm"):
+            raise ValueError("the parallel arrangement keeps the stream whole: its norm must offer stream_norm")
+        self.runtime, self.hidden = runtime, int(hidden_size)
+        self.mixer, self.mixer_norm, self.feed_forward = mixer, mixer_norm, feed_forward
+        self.gated, self.depth_states, self.history_slots, self.history_key = bool(gated), int(depth_states), int(history_slots), str(history_key)
+        outs = {"rg1": self.hidden, **({"rg2": self.hidden} if feed_forward is not None else {})}
+        self.gates = StackedLinear(runtime, self.hidden, outs) if self.gated else None
+        self.vectors: dict[str, torch.Tensor] = {}
+        self.gate_bias: torch.Tensor | None = None
+
+    def parts(self) -> dict[str, object]:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+        return out
+
+    def _vector_shapes(self) -> dict[str, tuple[int, ...]]:
+        out: dict[str, tuple[int, ...]] = {}
+        if self.gated:
+            out.update({name + ".b": (self.hidden,) for name in self.gates.outs})
+        if self.depth_states:
+            out["dwa"] = (self.depth_states,)
+        return out
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = dict(self.gates.parameters()) if self.gated else {}
+        out.update({name: ParamInfo(shape, role="vector") for name, shape in self._vector_shapes().items()})
+        return out
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if self.gated and name in self.gates.outs:
+            self.gates.assign(name, tensor)
+        elif name in self._vector_shapes():
+            self.vectors[name] = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+        else:
+            raise KeyError(name)
+
+    def finish_loading(self) -> None:
+        if self.gated:
+            self.gate_bias = torch.cat([self.vectors[name + ".b"] for name in self.gates.outs]).contiguous()
+
+    def forward(self, x, residual: torch.Tensor | None, ctx: StepContext, cache: LayerCache, defer_output: bool = False):
+        if residual is None:
+            if isinstance(x, DeferredLinear):
+                x = x.materialize()
+            if x.dtype != torch.float32:
+                raise ValueError("this arrangement keeps the stream in fp32: the embedding must hand it over whole")
+            stream = x
+        elif x is not None:
+            raise ValueError("this arrangement takes the stream whole; the block before it left an output that is not yet added")
+        else:
+            stream = residual
+        history = None
+        if self.depth_states:
+            history = ctx.shared.get(self.history_key)
+            if history is None:
+                # the first averaging block of the step: state 0 is the stream as it came from the embedding
+                history = torch.empty((self.history_slots, *stream.shape), dtype=torch.float32, device=stream.device)
+                history[0].copy_(stream)
+                ctx.shared[self.history_key] = history
+        h = self.mixer_norm.stream_norm(stream)
+        a_bias = None
+        if hasattr(self.mixer, "forward_parts"):
+            a, a_bias = self.mixer.forward_parts(h, ctx, cache)
+        else:
+            a = self.mixer.forward(h, ctx, cache)
+        f = self.feed_forward.forward(h) if self.feed_forward is not None else None
+        if f is not None and f.dtype != a.dtype:
+            f = ops.cast(f, a.dtype)
+        gates = self.gates(h) if self.gated else None
+        if gates is not None and gates.dtype != a.dtype:
+            gates = ops.cast(gates, a.dtype)
+        ops.gated_residual(stream, a, f, gates=gates, gate_bias=self.gate_bias, a_bias=a_bias, history=history, index=self.depth_states - 1,
+                           weights=self.vectors.get("dwa"))
         return None, stream

@@ -84,7 +84,12 @@ class DecoderModel:
                 if post_spec is not None:
                     post[key] = NORMS.build(post_spec.kind, runtime, **post_spec.params)
                     made.append((post[key], post_spec))
-            self.blocks.append(ARRANGEMENTS.build(layer.arrangement, mixer, mixer_norm, ff, ff_norm, **post))
+            if layer.block is not None:   # an arrangement with parameters and tensors of its own
+                block = ARRANGEMENTS.build(layer.block.kind, mixer, mixer_norm, ff, ff_norm, runtime=runtime, **layer.block.params, **post)
+                made.append((block, layer.block))
+            else:
+                block = ARRANGEMENTS.build(layer.arrangement, mixer, mixer_norm, ff, ff_norm, **post)
+            self.blocks.append(block)
             for part, part_spec in made:
                 if part is not None:
                     self._register(part, part_spec)

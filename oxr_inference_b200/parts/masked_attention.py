@@ -1,5 +1,6 @@
 """Attention mixers whose mask, sizes and extras are arguments: grouped-query attention within chunks with a bias by distance,
-and latent attention (one compressed row per token that serves as key and value of every head) with a softmax sink."""
+latent attention (one compressed row per token that serves as key and value of every head) with a softmax sink, and attention
+whose heads' scores are capped and mixed with each other before the softmax."""
 
 from __future__ import annotations
 
@@ -312,3 +313,95 @@ class LatentAttention(Mixer):
         o = torch.empty((n, H, self.DV), dtype=pool.dtype, device=pool.device)
         ops.head_linear(o, 0, o_lat, 0, self.uv)
         return self.out(o.view(n, H * self.DV))
+
+
+@MIXERS.register("mixed_head_attention")
+class MixedHeadAttention(Mixer):
+    """Grouped-query attention in which the heads see each other's scores. ``q, k, v = h W^T`` (+ ``q.b``, ``k.b``, ``v.b`` with ``biases``);
+    with a position encoding of rotated entry pairs, the first ``dims`` entries of every q and k head turn by the position's angles; the
+    scaled score ``s_g = (q_g . k) * scale`` is capped as ``softcap * tanh(s_g / softcap)`` (``softcap`` 0: not capped); with ``head_mix`` a
+    learned matrix ``talk [heads, heads]`` makes head h's score ``sum_g talk[h, g] s_g``; causal (``window`` > 0: the last ``window`` keys
+    only); ``unit_sink`` adds one to the softmax denominator (a place with score 0 that holds no value); with ``output_gate`` the
+    concatenated heads are multiplied by ``sigmoid(h W_g^T)`` (tensor ``g``) before ``W_o`` (+ ``o.b``). Every option stands alone.
+
+    q, k, v and the gate are one product. ``forward_parts`` returns the output projection's result and its bias apart, so that an
+    arrangement whose add takes a bias saves the pass over the rows."""
+
+    def __init__(self, runtime: Runtime, position: PositionEncoding | None, *, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int,
+                 value_dim: int, scale: float, biases: bool = False, softcap: float = 0.0, head_mix: bool = False, unit_sink: bool = False,
+                 output_gate: bool = False, window: int = 0):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} KV heads")
+        if position is not None and not hasattr(position, "step_angles"):
+            raise ValueError("mixed_head_attention rotates entry pairs by per-step angles (a position encoding with step_angles)")
+        if position is not None and position.dims > key_dim:
+            raise ValueError(f"{position.dims} rotated entries do not fit heads of {key_dim}")
+        if softcap < 0:
+            raise ValueError("softcap must not be negative (0 turns it off)")
+        self.runtime, self.position = runtime, position
+        self.hidden, self.H, self.KV, self.DK, self.DV = int(hidden_size), int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
+        self.scale, self.softcap, self.window = float(scale), float(softcap), int(window)
+        self.biases, self.head_mix, self.unit_sink, self.output_gate = bool(biases), bool(head_mix), bool(unit_sink), bool(output_gate)
+        self.cq, self.ck, self.cv = self.H * self.DK, self.KV * self.DK, self.KV * self.DV
+        outs = {"q": self.cq, "k": self.ck, "v": self.cv}
+        if self.output_gate:
+            outs["g"] = self.H * self.DV
+        self.qkvg = StackedLinear(runtime, self.hidden, outs)
+        self.out = StackedLinear(runtime, self.H * self.DV, {"o": self.hidden})
+        self.talk: torch.Tensor | None = None
+        self.vectors: dict[str, torch.Tensor] = {}
+        self.qkv_bias: torch.Tensor | None = None
+
+    def _vector_shapes(self) -> dict[str, tuple[int, ...]]:
+        if not self.biases:
+            return {}
+        return {"q.b": (self.cq,), "k.b": (self.ck,), "v.b": (self.cv,), "o.b": (self.hidden,)}
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = {**self.qkvg.parameters(), **self.out.parameters()}
+        if self.head_mix:
+            out["talk"] = ParamInfo((self.H, self.H), role="vector")
+        out.update({name: ParamInfo(shape, role="vector") for name, shape in self._vector_shapes().items()})
+        return out
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name in self.qkvg.outs:
+            self.qkvg.assign(name, tensor)
+        elif name in self.out.outs:
+            self.out.assign(name, tensor)
+        elif name == "talk" and self.head_mix:
+            self.talk = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+        elif name in self._vector_shapes():
+            self.vectors[name] = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+        else:
+            raise KeyError(name)
+
+    def finish_loading(self) -> None:
+        if self.biases:
+            v = self.vectors
+            self.qkv_bias = torch.cat([v["q.b"], v["k.b"], v["v.b"]]).contiguous()
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        y, bias = self.forward_parts(h, ctx, cache)
+        return y if bias is None else ops.add_bias_(y, bias)
+
+    def forward_parts(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """``(W_o o, o.b or None)``: the output without its bias, and the bias (fp32) for whoever adds next."""
+        group = cache.group
+        k_pool, v_pool = group.k_pool[cache.layer_in_group], group.v_pool[cache.layer_in_group]
+        proj = self.qkvg(h)
+        if proj.dtype != k_pool.dtype:
+            proj = ops.cast(proj, k_pool.dtype)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.step_angles(ctx)
+        ops.bias_rope_store(proj, self.cq, self.ck, self.cv, self.DK, bias=self.qkv_bias, cos=cos, sin=sin, k_pool=k_pool, v_pool=v_pool,
+                            slots=group.slots if cache.store else ctx.no_store_slots, status=ctx.status)
+        gate = proj[:, self.cq + self.ck + self.cv:] if self.output_gate else None
+        o = ops.attention_mix_rows(proj, self.H, k_pool, v_pool, positions=ctx.positions, req_of_token=ctx.req_of_token,
+                                   block_table=group.block_table, scale=self.scale, softcap=self.softcap, head_mix=self.talk,
+                                   unit_sink=self.unit_sink, window=self.window, gate=gate, status=ctx.status)
+        return self.out(o), (self.vectors["o.b"] if self.biases else None)

@@ -1,4 +1,4 @@
-"""Dense SiLU-gated feed-forward."""
+"""Dense feed-forwards: SiLU-gated, clamped gated, and a plain two-matrix layer with the tanh form of GELU."""
 
 from __future__ import annotations
 
@@ -70,3 +70,28 @@ class ClampedGLU(FeedForward):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         return self.down(ops.gated_linear(h, self.gate_up.weight, self.gate_up.interleave, kind="clamped", alpha=self.alpha, limit=self.limit))
+
+
+@FEED_FORWARDS.register("gelu_mlp")
+class GeluMLP(FeedForward):
+    """``down( gelu_tanh(h W_up^T) )`` with ``gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))``: two matrices, no gate, no
+    biases. The activation is evaluated in fp32 on the product's rounded output."""
+
+    def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int):
+        self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        self.up = StackedLinear(runtime, self.hidden, {"up": self.inter})
+        self.down = StackedLinear(runtime, self.inter, {"down": self.hidden})
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        return {**self.up.parameters(), **self.down.parameters()}
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name in self.up.outs:
+            self.up.assign(name, tensor)
+        elif name in self.down.outs:
+            self.down.assign(name, tensor)
+        else:
+            raise KeyError(name)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(ops.gelu_tanh_(self.up(h)))

@@ -1,4 +1,4 @@
-"""RMSNorm with the residual add fused in."""
+"""RMSNorm with the residual add fused in; layer norm (mean and variance, weight and bias) of a stream kept whole."""
 
 from __future__ import annotations
 
@@ -60,3 +60,38 @@ class RMSNorm(Norm):
         if then is None:
             return ops.norm_add_norm(stream, y, self.weight, self.eps)
         return ops.norm_add_norm(stream, y, self.weight, self.eps, then.weight, then.eps)
+
+
+@NORMS.register("layer_norm")
+class LayerNorm(Norm):
+    """``(x - mean(x)) / sqrt(var(x) + eps) * weight + bias`` with the variance as the mean of the squared deviations, computed in fp32 on
+    the fp32 stream. It serves arrangements that keep the stream whole (``stream_norm`` / ``stream_rows``); ``bias=False`` leaves the bias
+    tensor out."""
+
+    def __init__(self, runtime: Runtime, *, size: int, eps: float, bias: bool = True):
+        self.runtime, self.size, self.eps, self.has_bias = runtime, int(size), float(eps), bool(bias)
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = {"weight": ParamInfo((self.size,), init="around_one", role="vector")}
+        if self.has_bias:
+            out["bias"] = ParamInfo((self.size,), role="vector")
+        return out
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name not in self.parameters():
+            raise KeyError(name)
+        setattr(self, name, tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous())
+
+    def forward(self, x, residual):
+        raise ValueError("layer_norm normalises a stream that is kept whole in fp32 (stream_norm); it takes no pending block output")
+
+    def forward_rows(self, x, residual, rows):
+        raise ValueError("layer_norm normalises a stream that is kept whole in fp32 (stream_rows); it takes no pending block output")
+
+    def stream_norm(self, stream: torch.Tensor) -> torch.Tensor:
+        return ops.stream_layer_norm(stream, self.weight, self.bias, self.eps, self.runtime.dtype)
+
+    def stream_rows(self, stream: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        return ops.stream_layer_norm(stream, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)

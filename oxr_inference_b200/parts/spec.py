@@ -38,6 +38,9 @@ class LayerSpec:
     arrangement: str = "pre_norm"
     position: PartSpec | None = None
     """Position encoding handed to the mixer (shared between layers whose specs are equal)."""
+    block: PartSpec | None = None
+    """The arrangement as a part with sizes and tensors of its own (``kind`` then replaces ``arrangement``; its constructor also receives
+    the runtime): gates on the sublayers' results, weights over earlier layers' results and the like."""
     mixer_post_norm: PartSpec | None = None
     """Norm of the mixer's output before it joins the stream (arrangements with a norm on both sides of a sublayer)."""
     feed_forward_post_norm: PartSpec | None = None
