@@ -158,3 +158,15 @@ def forward(cfg: dict, w: dict, ids: list[int], layers_out: list | None = None, 
             layers_out.append(x)
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
     return x @ w["head"].T
+
+
+def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> tuple[list[int], list[float]]:
+    """``n`` greedy tokens after ``prompt``, and for each the gap between the two largest logits over the logits' spread (a near-tie
+    may fall either way under another rounding)."""
+    ids, gaps = list(prompt), []
+    for _ in range(n):
+        row = forward(cfg, w, ids)[-1]
+        best = row.topk(2).values
+        gaps.append(float((best[0] - best[1]) / row.std()))
+        ids.append(int(row.argmax()))
+    return ids[len(prompt):], gaps
