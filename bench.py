@@ -612,6 +612,196 @@ def bifusun_workload(args) -> int:
     return 0
 
 
+def vazepel_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int, layers: int, vocab: int, experts: int = 16, top: int = 4) -> dict:
+    """A Vazepel model of a real model's layer sizes: parallel blocks whose attention (biases, rotated pairs, capped and mixed scores, a
+    unit sink, an output gate) has the head sizes of the Qwen3 model beside it; the feed-forwards are, in turn, a two-matrix GELU layer with
+    as many weights as the gated one beside it (half as wide again) and experts (``top`` of ``experts``, each an eighth of ``ff`` wide, with a
+    shared expert of half of ``ff``: a token runs ``ff`` columns in all)."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "softcap": 30.0,
+             "rot": {"dims": head_dim // 2, "base": 10000.0}}
+    dense = {"kind": "dense", "ff": ff * 3 // 2}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top), "limit": 7.0}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": ff // 2, "limit": 7.0}}
+    return {"architecture": "Vazepel", "norm": {"eps": 1e-5}, "vocab": vocab, "width": width,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": (dense, moe)[i % 2]} for i in range(layers)]}
+
+
+def vazepel_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: int) -> list[dict]:
+    """Each kernel of the design alone, at one model size, beside the like kernel of the Qwen3 path: device time (median, L2 flushed
+    between calls), the bytes or FLOPs it has to move or do, and the fraction of the measured peak."""
+    import torch
+
+    from oxr_inference_b200 import ops
+
+    dev = "cuda"
+    hbm_gbs, bf16_tflops, _ = peaks()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    status = ops.new_status(dev)
+    bf = torch.bfloat16
+    rows = []
+
+    def put(name, like, ms, *, bytes_=None, flops=None):
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            row.update(gb_s=round(bytes_ / (ms * 1e-3) / 1e9, 1), frac=round(bytes_ / (ms * 1e-3) / 1e9 / hbm_gbs, 4), bound="hbm")
+        else:
+            row.update(tflop_s=round(flops / (ms * 1e-3) / 1e12, 2), frac=round(flops / (ms * 1e-3) / 1e12 / bf16_tflops, 4), bound="tensor")
+        rows.append(row)
+
+    P, T, B, CTX = 16, 2048, 8, 2048
+    H, KV, D = heads, kv_heads, head_dim
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rand(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    n_pages = B * (CTX // P) + T // P + 8
+    k_pool, v_pool = rand(n_pages, P, KV, D), rand(n_pages, P, KV, D)
+    cq, ck, cv = H * D, KV * D, KV * D
+    C = cq + ck + cv + cq      # q | k | v | output gate
+    mix = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, generator=g, device=dev)).contiguous()
+    bias = rand(cq + ck + cv, dtype=torch.float32)
+    ones = torch.ones(D, device=dev)
+    cos_table = torch.ones(8192, D // 2, device=dev)
+    tile = ops.attention_mix_tile(H, KV, D, D, bf)
+    maps = ops.make_kv_maps(k_pool.unsqueeze(0), v_pool.unsqueeze(0), P)
+    for name, q_lens, ctx_lens in (("prefill 2048", [T], [T]), ("decode b8", [1] * B, [CTX] * B)):
+        n, prefill = sum(q_lens), q_lens[0] > 1
+        proj = rand(n, C, scale=0.5)
+        cu = i32([0] + list(torch.tensor(q_lens).cumsum(0)))
+        req = torch.repeat_interleave(torch.arange(len(q_lens), dtype=torch.int32), torch.tensor(q_lens)).to(dev)
+        pos = i32(list(range(T)) if prefill else [CTX - 1] * B)
+        slots = i32([(r * (CTX // P)) * P + (i if prefill else CTX - 1) for r, x in enumerate(q_lens) for i in range(x)])
+        table = torch.stack([torch.arange(r * (CTX // P), r * (CTX // P) + CTX // P + 1, dtype=torch.int32) % n_pages for r in range(len(q_lens))]).to(dev).contiguous()
+        # ---- between the product and attention
+        qkv = proj[:, :cq + ck + cv].contiguous()
+        ms = _time_ms(lambda: ops.qk_norm_rope_store(qkv, ones, ones, cos_table, cos_table, pos, slots, k_pool, v_pool, H, KV, D, 1e-6, status), flush=flush)
+        put(f"qk_norm_rope_store {name}", None, ms, bytes_=n * (cq + ck + cv) * 2 * 2)
+        cos = torch.ones(n, D // 4, device=dev)
+        ms = _time_ms(lambda: ops.bias_rope_store(proj, cq, ck, cv, D, bias=bias, cos=cos, sin=cos, k_pool=k_pool, v_pool=v_pool, slots=slots, status=status), flush=flush)
+        put(f"bias_rope_store {name} (biases, rotated pairs, cache write)", f"qk_norm_rope_store {name}", ms, bytes_=n * (cq + ck + cv) * 2 * 2)
+        # ---- attention
+        def tiles_for(spec):
+            r_ = [r for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for _ in range(0, x, spec[0])]
+            t_ = [t0 for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for t0 in range(0, x, spec[0])]
+            return i32(r_ + [0]), i32(t_ + [0]), len(r_)
+        q3 = rand(n, H, D)
+        for tma in (True, False):
+            specs = ops.attention_tile_specs(H, KV, D, bf, P if tma else None)
+            args = dict(tiles={spec: tiles_for(spec) for spec in specs}, cu_q=cu, ctx_lens=i32(ctx_lens), block_table=table, page_size=P, scale=D ** -0.5,
+                        window=0, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps if tma else None)
+            ms = _time_ms(lambda: ops.paged_attention(q3, k_pool, v_pool, **args), flush=flush)
+            kind = ("tcgen05, TMA" if prefill else "TMA split-KV") if tma else ("cp.async mma" if prefill else "cp.async split-KV")
+            if prefill:
+                put(f"paged_attention {name} ({kind})", None, ms, flops=2 * 2 * H * D * T * (T + 1) // 2)
+            else:
+                put(f"paged_attention {name} ({kind})", None, ms, bytes_=sum(ctx_lens) * KV * 2 * D * 2)
+        like = f"paged_attention {name} ({'cp.async mma' if prefill else 'cp.async split-KV'})"
+        common = dict(positions=pos, block_table=table, scale=D ** -0.5, softcap=30.0, head_mix=mix, unit_sink=True, gate=proj[:, cq + ck + cv:], status=status)
+        ms = _time_ms(lambda: ops.attention_mix_tiled(proj, H, k_pool, v_pool, tile=tile, tiles=tiles_for((tile[0], 1, 1 << 30)), cu_q=cu,
+                                                      kv_len_bound=max(ctx_lens), **common), flush=flush)
+        pairs = T * (T + 1) // 2 if prefill else sum(ctx_lens)
+        if prefill:
+            # q k and p v on the tensor cores, and the H x H mix of every (query, key) place on the fp32 pipes
+            put(f"attention_mix_tiled {name} (cap, {H} x {H} mix, sink, gate; mma.sync)", like, ms, flops=pairs * (2 * 2 * H * D + 2 * H * H))
+        else:
+            put(f"attention_mix_tiled {name} (cap, {H} x {H} mix, sink, gate; split keys)", like, ms, bytes_=pairs * KV * 2 * D * 2)
+        if not prefill:
+            ms = _time_ms(lambda: ops.attention_mix_rows(proj, H, k_pool, v_pool, req_of_token=req, **common), flush=flush)
+            put(f"attention_mix_rows {name} (the 32-bit kernel, on bfloat16 rows)", like, ms, bytes_=pairs * KV * 2 * D * 2)
+        # ---- the stream: norm, and the gated add with the depth average
+        stream, w, b = torch.randn(n, width, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
+        x = rand(n, width)
+        ms = _time_ms(lambda: ops.add_rms_norm(x, stream, w, 1e-6), flush=flush)
+        put(f"add_rms_norm {name}", None, ms, bytes_=n * width * (2 + 4 + 4 + 2))
+        ms = _time_ms(lambda: ops.stream_layer_norm(stream, w, b, 1e-5, bf), flush=flush)
+        put(f"stream_layer_norm {name}", f"add_rms_norm {name}", ms, bytes_=n * width * (4 + 2))
+        depth = 5
+        history = torch.randn(depth + 1, n, width, device=dev)
+        a, f_, gates = rand(n, width), rand(n, width), rand(n, 2 * width)
+        gb, ab, dw = torch.zeros(2 * width, device=dev), torch.zeros(width, device=dev), torch.full((depth + 1,), 0.2, device=dev)
+        ms = _time_ms(lambda: ops.gated_residual(stream, a, f_, gates=gates, gate_bias=gb, a_bias=ab, history=history, index=depth, weights=dw), flush=flush)
+        put(f"gated_residual {name} (two gates, both adds, history of {depth + 1}, weighted sum)", f"add_rms_norm {name}", ms,
+            bytes_=n * width * (4 + 2 + 2 + 4 + 4 + depth * 4 + 4))
+        # ---- feed-forward activations
+        gu = rand(n, 2 * ff)
+        ms = _time_ms(lambda: ops.silu_mul(gu), flush=flush)
+        put(f"silu_mul {name}", None, ms, bytes_=n * ff * 6)
+        up = rand(n, ff * 3 // 2)
+        ms = _time_ms(lambda: ops.gelu_tanh_(up), flush=flush)
+        put(f"gelu_tanh {name} (in place)", f"silu_mul {name}", ms, bytes_=n * (ff * 3 // 2) * 4)
+        ms = _time_ms(lambda: ops.clamped_glu(gu, alpha=1.702, limit=7.0), flush=flush)
+        put(f"clamped_glu {name} (the shared expert)", f"silu_mul {name}", ms, bytes_=n * ff * 6)
+        E, top = 16, 4
+        z = torch.randn(n, E, device=dev)
+        ms = _time_ms(lambda: ops.route(z, top=top, groups=8, keep=4, scale=2.0), flush=flush)
+        put(f"route {name} (sigmoid, best two of a group)", None, ms, bytes_=n * (E * 8 + top * 8))
+        ms = _time_ms(lambda: ops.route(z, top=top, groups=4, keep=2, scale=1.0, score="softmax", group_score="max", renormalize=False), flush=flush)
+        put(f"route {name} (softmax, best of a group, scores as weights)", f"route {name} (sigmoid, best two of a group)", ms, bytes_=n * (E * 8 + top * 8))
+    # ---- the feed-forwards as a whole, beside the dense gated one
+    from oxr_inference_b200.parts.base import FEED_FORWARDS, Runtime
+
+    rt = Runtime(device=torch.device(dev), dtype=bf, max_positions=1, status=status)
+    E, top, ffe = 16, 4, ff // 8
+    gate_up_w, dense_down_w = rand(2 * ff, width, scale=0.02), rand(width, ff, scale=0.02)
+    gelu = FEED_FORWARDS.build("gelu_mlp", rt, hidden_size=width, intermediate_size=ff * 3 // 2)
+    gelu.assign("up", rand(ff * 3 // 2, width, scale=0.02)); gelu.assign("down", rand(width, ff * 3 // 2, scale=0.02))
+    unit = {"hidden_size": width, "intermediate_size": ff // 2, "limit": 7.0, "alpha": 1.702}
+    moe = FEED_FORWARDS.build("routed_experts", rt, hidden_size=width, intermediate_size=ffe, experts=E, top=top, groups=4, keep=2, activation="clamped_glu",
+                              limit=7.0, score="softmax", group_score="max", renormalize=False, shared={"kind": "clamped_glu", "params": unit})
+    for name, info in moe.parameters().items():
+        moe.assign(name, rand(*info.shape, scale=0.02))
+    for part in (gelu, moe):
+        part.finish_loading()
+    for n in (T, B):
+        h = rand(n, width)
+        dense_name = f"dense gated feed-forward {n} rows (three products of {ff})"
+        ms = _time_ms(lambda: ops.linear(ops.silu_mul(ops.linear(h, gate_up_w)), dense_down_w), flush=flush)
+        weights_dense = 3 * ff * width * 2
+        put(dense_name, None, ms, **({"flops": 2 * n * width * 3 * ff} if n >= 256 else {"bytes_": weights_dense}))
+        ms = _time_ms(lambda: gelu.forward(h), flush=flush)
+        put(f"GELU feed-forward {n} rows (two products of {ff * 3 // 2})", dense_name, ms,
+            **({"flops": 2 * n * width * 3 * ff} if n >= 256 else {"bytes_": weights_dense}))
+        ms = _time_ms(lambda: moe.forward(h), flush=flush)
+        touched = E * (1 - (1 - top / E) ** n)
+        put(f"routed clamped experts {n} rows ({top} of {E} of {ffe}, shared {ff // 2})", dense_name, ms,
+            **({"flops": 2 * n * width * 3 * ff} if n >= 256 else {"bytes_": 3 * width * 2 * (touched * ffe + ff // 2)}))
+    ops.check_status(status)
+    return rows
+
+
+def vazepel_workload(args) -> int:
+    """The Vazepel design beside Qwen3 at equal sizes: whole-model prefill and decode throughput at two sizes, and every kernel of the new
+    parts against its roofline beside the like kernel of the Qwen3 path."""
+    import torch
+
+    sizes = [("2048 wide, 8 layers", dict(width=2048, ff=8192, heads=16, kv_heads=4, head_dim=128, layers=8, vocab=32768)),
+             ("4096 wide, 8 layers (Qwen3-8B layer sizes)", dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=8, vocab=32768))]
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {"workload": "vazepel", "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)", "steps": K, "warmup": W,
+           "batch": 8, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks()[2], "sizes": []}
+    for name, s in sizes:
+        qwen = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": s["width"], "intermediate_size": s["ff"],
+                "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
+                "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": s["vocab"], "tie_word_embeddings": False,
+                "max_position_embeddings": 8192}
+        row = {"size": name}
+        for design, cfg in (("qwen3", qwen), ("vazepel", vazepel_config(**s))):
+            row[design] = design_throughput(cfg, s["vocab"], K, W, 8, args.context, PREFILL_TOKENS)
+            torch.cuda.empty_cache()
+        out["sizes"].append(row)
+    last = sizes[-1][1]
+    out["kernels"] = vazepel_kernels(last["width"], last["heads"], last["kv_heads"], last["head_dim"], last["ff"])
+    out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -622,9 +812,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the further points (quick runs)")
     ap.add_argument("--skip-serving", action="store_true", help="leave the two serving workloads out of `points`")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
-    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel", "bifusun"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel", "bifusun", "vazepel"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each; "
-                         "radapel / bifusun: that design beside Qwen3 at equal sizes, whole models and kernel by kernel")
+                         "radapel / bifusun / vazepel: that design beside Qwen3 at equal sizes, whole models and kernel by kernel")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -635,6 +825,8 @@ def main() -> int:
         return radapel_workload(args)
     if args.workload == "bifusun":
         return bifusun_workload(args)
+    if args.workload == "vazepel":
+        return vazepel_workload(args)
     if args.workload != "decode":
         return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)

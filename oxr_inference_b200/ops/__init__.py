@@ -156,6 +156,10 @@ def _lib():
         lib.oxr_add_inplace.restype = c_int
         lib.oxr_attention_mix_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, f, p, i, i, p, i, i, p, p]
         lib.oxr_bias_rope_store.argtypes = [p, i, i, i, i, i, p, p, p, i, p, p, ll, p, i, i, p, p]
+        lib.oxr_attention_mix_mma.argtypes = [p, p, i, p, p, i, i, i, i, i, p, p, i, p, p, i, p, i, i, i, f, f, p, i, i, p, i, i, p, p, p, p]
+        lib.oxr_attention_mix_mma.restype = c_int
+        lib.oxr_attention_mix_mma_smem.argtypes = [i, i, i, i, i]
+        lib.oxr_attention_mix_mma_smem.restype = c_longlong
         lib.oxr_expert_clamped_glu.argtypes = [p, p, p, i, i, i, f, f, i, p]
         for name in ("oxr_stream_layer_norm", "oxr_gated_residual", "oxr_gelu_tanh", "oxr_attention_mix_rows", "oxr_bias_rope_store",
                      "oxr_expert_clamped_glu"):
@@ -1243,6 +1247,84 @@ def attention_mix_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_
                                         pages, float(scale), float(softcap), _ptr(head_mix), int(bool(unit_sink)), int(window),
                                         gate.data_ptr() if gate is not None else None, gate_stride, _dtype_code(q), status.data_ptr(), _stream()),
           "attention_mix_rows")
+    return out
+
+
+MIX_TILE_SMEM_LIMIT = 227 * 1024
+MIX_TILE_KEYS = 16
+"""Keys per block of the tiled head-mixing kernel."""
+
+
+def attention_mix_tile(num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, dtype: torch.dtype) -> tuple[int, int] | None:
+    """``(query tokens per tile, query parts per block)`` with which the tensor-core kernel of head-mixing attention takes these sizes, or None
+    when it does not (then ``attention_mix_rows`` is the kernel): bfloat16, keys and values of 64 or 128, 1, 2, 4, 8 or 16 query heads per
+    key/value head (a 16-row MMA tile then holds 16 / that many queries of one key/value head), at most 16 key/value heads (one warp each per
+    query part). The block takes as many query parts as 16 warps and its shared memory allow."""
+    H, KV, DK, DV = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
+    if dtype != torch.bfloat16 or KV <= 0 or H % KV or DK not in (64, 128) or DV not in (64, 128) or KV > 16:
+        return None
+    per = H // KV
+    if per > 16 or 16 % per:
+        return None
+    rows_per_part, padded_heads = 16 // per, (H + 3) & ~3
+    for parts in range(16 // KV, 0, -1):
+        # queries, one K and one V block of all key/value heads (rows padded by 8), the heads' scores, the mixing matrix, two slot lists
+        need = (KV * parts * 16 * (DK + 8) * 2 + KV * MIX_TILE_KEYS * (DK + 8 + DV + 8) * 2 + padded_heads * parts * rows_per_part * MIX_TILE_KEYS * 4
+                + H * padded_heads * 4 + 2 * MIX_TILE_KEYS * 8)
+        if need <= MIX_TILE_SMEM_LIMIT:
+            return parts * rows_per_part, parts
+    return None
+
+
+def attention_mix_splits(n_tiles: int, kv_len_bound: int) -> int:
+    """Pieces into which the tiled head-mixing kernel cuts every tile's keys: enough blocks for all SMs, at least four key blocks each."""
+    if n_tiles <= 0:
+        return 1
+    most = max(1, -(-int(kv_len_bound) // MIX_TILE_KEYS) // 4)
+    return max(1, min(most, num_sms() // n_tiles, 64))
+
+
+def attention_mix_tiled(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, *, tile: tuple[int, int],
+                        tiles: tuple[torch.Tensor, torch.Tensor, int], cu_q: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                        kv_len_bound: int, scale: float, softcap: float = 0.0, head_mix: torch.Tensor | None = None, unit_sink: bool = False,
+                        window: int = 0, gate: torch.Tensor | None = None, status: torch.Tensor, splits: int | None = None) -> torch.Tensor:
+    """The function of :func:`attention_mix_rows` in bfloat16 on the tensor cores. ``tile`` is what :func:`attention_mix_tile` gave for
+    the sizes; ``tiles = (tile_req, tile_tok0, count)`` cuts every request's new tokens into runs of ``tile[0]`` tokens (the batch builder's
+    list for the spec ``(tile[0], 1, any)``); ``kv_len_bound`` bounds every request's context and, with the number of tiles, decides into
+    how many pieces the keys are cut (``splits`` overrides it). Scores, the mixing, the softmax weights and all sums are fp32; the weights
+    are rounded to bfloat16 for the product with the values."""
+    global launch_count
+    _need(q, "q", torch.bfloat16)
+    _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16)
+    n, H = q.shape[0], int(num_heads)
+    pages, page_size, KV, DK = k_pool.shape
+    DV = v_pool.shape[3]
+    if q.dim() != 2 or q.shape[1] < H * DK or v_pool.shape[:3] != k_pool.shape[:3] or q.shape[1] % 8 or q.data_ptr() % 16:
+        raise KernelError("attention_mix_tiled: sizes do not fit")
+    if head_mix is not None:
+        _need(head_mix, "head_mix", torch.float32)
+        if head_mix.shape != (H, H):
+            raise KernelError("attention_mix_tiled: the mixing matrix must be [heads, heads]")
+    gate_stride = 0
+    if gate is not None:
+        if gate.dtype != q.dtype or gate.shape != (n, H * DV) or gate.stride(1) != 1 or not gate.is_cuda or gate.data_ptr() % 4:
+            raise KernelError("attention_mix_tiled: the gate does not fit")
+        gate_stride = gate.stride(0)
+    tile_req, tile_tok0, n_tiles = tiles
+    if splits is None:
+        splits = attention_mix_splits(n_tiles, kv_len_bound)
+    out = torch.empty((n, H * DV), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n, splits, H * DV), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n, splits, H, 2), dtype=torch.float32, device=q.device)
+    _done(_lib().oxr_attention_mix_mma(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), DK, DV, H, KV, int(tile[1]),
+                                       tile_req.data_ptr(), tile_tok0.data_ptr(), int(n_tiles), cu_q.data_ptr(), positions.data_ptr(), n,
+                                       block_table.data_ptr(), block_table.shape[1], page_size, pages, float(scale), float(softcap), _ptr(head_mix),
+                                       int(bool(unit_sink)), int(window), gate.data_ptr() if gate is not None else None, gate_stride, int(splits),
+                                       _ptr(part_o), _ptr(part_ml), status.data_ptr(), _stream()), "attention_mix_tiled")
+    launch_count += 1 if splits > 1 else 0   # the pieces' combine
     return out
 
 

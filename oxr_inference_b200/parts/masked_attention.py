@@ -384,6 +384,16 @@ class MixedHeadAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV)
 
+    @property
+    def tile(self) -> tuple[int, int] | None:
+        """(tokens per tile, query parts per block) of the tensor-core kernel, None where the sizes or the dtype leave the rows kernel."""
+        if not hasattr(self, "_tile"):
+            self._tile = ops.attention_mix_tile(self.H, self.KV, self.DK, self.DV, self.runtime.dtype)
+        return self._tile
+
+    def tile_specs(self) -> list[tuple[int, int, int]]:
+        return [(self.tile[0], 1, 1 << 30)] if self.tile is not None else []
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         y, bias = self.forward_parts(h, ctx, cache)
         return y if bias is None else ops.add_bias_(y, bias)
@@ -401,6 +411,12 @@ class MixedHeadAttention(Mixer):
         ops.bias_rope_store(proj, self.cq, self.ck, self.cv, self.DK, bias=self.qkv_bias, cos=cos, sin=sin, k_pool=k_pool, v_pool=v_pool,
                             slots=group.slots if cache.store else ctx.no_store_slots, status=ctx.status)
         gate = proj[:, self.cq + self.ck + self.cv:] if self.output_gate else None
+        if self.tile is not None and proj.dtype == torch.bfloat16:
+            o = ops.attention_mix_tiled(proj, self.H, k_pool, v_pool, tile=self.tile, tiles=ctx.tiles[self.tile_specs()[0]], cu_q=ctx.cu_q,
+                                        positions=ctx.positions, block_table=group.block_table, kv_len_bound=ctx.kv_len_bound, scale=self.scale,
+                                        softcap=self.softcap, head_mix=self.talk, unit_sink=self.unit_sink, window=self.window, gate=gate,
+                                        status=ctx.status)
+            return self.out(o), (self.vectors["o.b"] if self.biases else None)
         o = ops.attention_mix_rows(proj, self.H, k_pool, v_pool, positions=ctx.positions, req_of_token=ctx.req_of_token,
                                    block_table=group.block_table, scale=self.scale, softcap=self.softcap, head_mix=self.talk,
                                    unit_sink=self.unit_sink, window=self.window, gate=gate, status=ctx.status)

@@ -138,7 +138,7 @@ def test_layer_results_one_by_one(tmp_path):
 
 
 # ------------------------------------------------------------------------------------------------ whole models, every cutting
-MODELS = {"P": VU.MODEL_P, "Q": VU.MODEL_Q, "R": VU.MODEL_R}
+MODELS = {"P": VU.MODEL_P, "Q": VU.MODEL_Q, "R": VU.MODEL_R, "T": VU.MODEL_T}
 
 
 @pytest.fixture(scope="module", params=[(m, d) for m in sorted(MODELS) for d in ("float32", "bfloat16")], ids=lambda p: f"{p[0]}-{p[1]}")
@@ -311,3 +311,82 @@ def test_bfloat16_generation_with_graphs_equals_eager(tmp_path):
         engine = Engine(folder, EngineSettings(dtype="bfloat16", num_pages=48, page_size=16, max_running=4, cuda_graphs=graphs))
         out.append([c.token_ids for c in engine.generate(prompts, SamplingParams(max_tokens=10, ignore_eos=True))])
     assert out[0] == out[1]
+
+
+# ------------------------------------------------------------------------------------------------ the tensor-core attention kernel alone
+def plain_mixed_attention(q, k, v, pos, ctx_of, *, scale, cap, mix, sink, window, gate):
+    """One request: q [n, H, DK] at positions pos, keys / values k, v [ctx, KV, D*] (fp64), by the formulas."""
+    n, H, _ = q.shape
+    per = H // k.shape[1]
+    s = torch.einsum("ihd,jhd->hij", q, k.repeat_interleave(per, 1)) * scale
+    if cap > 0:
+        s = cap * torch.tanh(s / cap)
+    if mix is not None:
+        s = torch.einsum("hg,gij->hij", mix, s)
+    j = torch.arange(ctx_of)
+    seen = j[None, :] <= pos[:, None]
+    if window > 0:
+        seen &= j[None, :] > pos[:, None] - window
+    e = torch.where(seen[None], torch.exp(s - s.amax(-1, keepdim=True)), torch.zeros_like(s))
+    denom = e.sum(-1) + (torch.exp(-s.amax(-1)) if sink else 0.0)
+    o = torch.einsum("hij,jhd->ihd", e / denom[..., None], v.repeat_interleave(per, 1))
+    if gate is not None:
+        o = o * torch.sigmoid(gate)
+    return o
+
+
+@pytest.mark.parametrize("H,KV,DK,DV", [(8, 2, 64, 128), (4, 4, 128, 64), (16, 1, 64, 64), (6, 3, 128, 128), (32, 8, 128, 128), (2, 1, 64, 64)])
+@pytest.mark.parametrize("window,splits", [(0, None), (0, 3), (37, 1), (21, 2)])
+def test_tiled_kernel_against_the_formulas(H, KV, DK, DV, window, splits):
+    """Requests of unequal lengths and portions (one token, two, a run that ends inside a tile, a long one) over pages dealt out in a
+    shuffled order; the keys in one piece and in several; with and without a window; the mix far from the identity."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(H * 1000 + DK + window)
+    tile = ops.attention_mix_tile(H, KV, DK, DV, torch.bfloat16)
+    assert tile is not None
+    P, ctx_lens, q_lens = 8, [70, 1, 131, 19, 45], [1, 1, 67, 2, 45]
+    n_pages = sum(-(-c // P) for c in ctx_lens) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    k_pool = torch.zeros(n_pages, P, KV, DK, dtype=torch.bfloat16)
+    v_pool = torch.zeros(n_pages, P, KV, DV, dtype=torch.bfloat16)
+    width = max(-(-c // P) for c in ctx_lens)
+    table = torch.full((len(ctx_lens), width), -1, dtype=torch.int32)
+    mix = (torch.eye(H) + 0.4 * torch.randn(H, H, generator=g)).bfloat16().float()
+    scale, cap = 0.5 * DK ** -0.5, 7.0
+    qs, gates, pos, wants = [], [], [], []
+    for r, (c, ql) in enumerate(zip(ctx_lens, q_lens)):
+        k = (torch.randn(c, KV, DK, generator=g) * 1.5).bfloat16()
+        v = torch.randn(c, KV, DV, generator=g).bfloat16()
+        for j in range(c):
+            page = order.pop() if j % P == 0 else int(table[r, j // P])
+            table[r, j // P] = page
+            k_pool[page, j % P], v_pool[page, j % P] = k[j], v[j]
+        q = (torch.randn(ql, H, DK, generator=g) * 1.5).bfloat16()
+        gate = torch.randn(ql, H, DV, generator=g).bfloat16()
+        p_r = torch.arange(c - ql, c)
+        wants.append(plain_mixed_attention(q.double(), k.double(), v.double(), p_r, c, scale=scale, cap=cap, mix=mix.double(), sink=True,
+                                           window=window, gate=gate.double()).reshape(ql, H * DV))
+        qs.append(q.reshape(ql, H * DK)); gates.append(gate.reshape(ql, H * DV)); pos.append(p_r)
+    n = sum(q_lens)
+    # q and the gate as columns of one stacked row, as the mixer hands them over
+    proj = torch.cat([torch.cat(qs), torch.zeros(n, 24, dtype=torch.bfloat16), torch.cat(gates)], 1).to(DEV)
+    treq, ttok = [], []
+    for r, ql in enumerate(q_lens):
+        for t0 in range(0, ql, tile[0]):
+            treq.append(r); ttok.append(t0)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    cu = i32([0] + torch.tensor(q_lens).cumsum(0).tolist())
+    status = ops.new_status(DEV)
+    common = dict(positions=torch.cat(pos).to(DEV, torch.int32), block_table=table.to(DEV), scale=scale, softcap=cap, head_mix=mix.to(DEV),
+                  unit_sink=True, window=window, gate=proj[:, H * DK + 24:], status=status)
+    got = ops.attention_mix_tiled(proj, H, k_pool.to(DEV), v_pool.to(DEV), tile=tile, tiles=(i32(treq), i32(ttok), len(treq)), cu_q=cu,
+                                  kv_len_bound=max(ctx_lens), splits=splits, **common)
+    rows = ops.attention_mix_rows(proj, H, k_pool.to(DEV), v_pool.to(DEV), req_of_token=torch.repeat_interleave(torch.arange(len(q_lens)), torch.tensor(q_lens)).to(DEV, torch.int32),
+                                  **common)
+    ops.check_status(status)
+    want = torch.cat(wants).float()
+    err = (got.float().cpu() - want).abs().max() / want.abs().max()
+    err_rows = (rows.float().cpu() - want).abs().max() / want.abs().max()
+    assert err_rows < 1e-2, f"the rows kernel is off by {err_rows:.2e}"
+    assert err < 1.5e-2, f"the tiled kernel is off by {err:.2e} of the largest entry (the rows kernel: {err_rows:.2e})"

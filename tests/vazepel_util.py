@@ -46,6 +46,13 @@ MODEL_Q = model_config([layer(heads=4, kv_heads=1, dim=64, vdim=64, rot=64, base
 MODEL_R = model_config([layer(heads=5, kv_heads=5, dim=24, vdim=8, rot=2, scale=0.25, softcap=4.0, mlp=moe(ff=32, experts=9, top=2, count=3, keep=1, shared=16)),
                         layer(heads=1, kv_heads=1, dim=70, vdim=40, rot=34, base=50.0, scale=0.12, softcap=9.0, mlp=moe(ff=12, experts=5, top=5, count=1, keep=1))],
                        width=40, vocab=97)
+# Every layer has key and value sizes that the tensor-core attention kernel takes in bfloat16, with 4, 1, 16 and 2 query heads per key/value
+# head (6 heads: the mixing matrix is padded), key sizes unlike value sizes, few and all entries rotated.
+MODEL_T = model_config([layer(heads=8, kv_heads=2, dim=64, vdim=128, rot=40, scale=0.14, softcap=20.0, mlp=dense(ff=40)),
+                        layer(heads=2, kv_heads=2, dim=128, vdim=64, rot=128, base=5000.0, scale=0.1, softcap=3.0, mlp=moe(ff=16, experts=4, top=2, count=2, keep=1, shared=24)),
+                        layer(heads=16, kv_heads=1, dim=64, vdim=64, rot=6, scale=0.13, softcap=8.0),
+                        layer(heads=6, kv_heads=3, dim=64, vdim=64, rot=64, scale=0.12, softcap=50.0, mlp=dense(ff=32))],
+                       width=56, vocab=150, eps=1e-5)
 
 
 def make_folder(tmp: Path, config: dict, name: str, seed: int = 0, sharpen: float = 8.0) -> Path:
