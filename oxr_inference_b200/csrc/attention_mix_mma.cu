@@ -47,8 +47,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// tanh(y) = 1 - 2 / (exp(2y) + 1): absolute error of a few 1e-7 everywhere, exact limits at both ends
-__device__ __forceinline__ float tanh_exp(float y) { return 1.f - __fdividef(2.f, __expf(2.f * y) + 1.f); }
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float LOG2E = 1.4426950408889634f;
+// cap * tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1), with x = raw * scale and k2 = 2 * scale / cap * log2(e): absolute error of
+// a few 1e-7 of cap everywhere, exact limits at both ends (exp = inf: cap; exp = 0: -cap)
+__device__ __forceinline__ float capped(float raw, float k2, float cap) { return fmaf(-2.f * cap, rcp_fast(ex2_fast(raw * k2) + 1.f), cap); }
 
 struct MixArgs {
     bf16* out;
@@ -56,7 +68,7 @@ struct MixArgs {
     int q_stride;
     const bf16* k_pool;
     const bf16* v_pool;
-    int H, KVH, HP, QT;
+    int H, KVH, HP, QT, SQ;   // SQ: query rows per head in the score exchange (QT * R, or 1 when every tile is one token)
     const int* tile_req;
     const int* tile_tok0;
     const int* cu_q;
@@ -74,8 +86,8 @@ struct MixArgs {
     int* status;
 };
 
-__host__ __device__ inline size_t mix_smem_bytes(int DK, int DV, int H, int KVH, int HP, int QT) {
-    const int per = H / KVH, R = 16 / per, BM = QT * R, warps = KVH * QT;
+__host__ __device__ inline size_t mix_smem_bytes(int DK, int DV, int H, int KVH, int HP, int QT, int SQ) {
+    const int BM = SQ, warps = KVH * QT;
     return (size_t)warps * 16 * (DK + PADE) * 2 + (size_t)KVH * BN * (DK + PADE) * 2 + (size_t)KVH * BN * (DV + PADE) * 2 +
            (size_t)HP * BM * BN * 4 + (size_t)H * HP * 4 + 2 * BN * sizeof(long long);
 }
@@ -85,17 +97,17 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
     extern __shared__ __align__(16) unsigned char mix_mma_smem[];
     constexpr int LQ = DK + PADE, LV = DV + PADE;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x;
-    const int H = p.H, KVH = p.KVH, per = H / KVH, R = 16 / per, QT = p.QT, BM = QT * R, HP = p.HP;
+    const int H = p.H, KVH = p.KVH, per = H / KVH, R = 16 / per, QT = p.QT, BM = QT * R, HP = p.HP, SQ = p.SQ;
     const int n_warps = KVH * QT;
     bf16* Qs = reinterpret_cast<bf16*>(mix_mma_smem);              // [warps][16][LQ]
     bf16* Ks = Qs + (size_t)n_warps * 16 * LQ;                     // [KVH][BN][LQ]
     bf16* Vs = Ks + (size_t)KVH * BN * LQ;                         // [KVH][BN][LV]
-    float* Ss = reinterpret_cast<float*>(Vs + (size_t)KVH * BN * LV);   // [HP][BM][BN], a thread's columns side by side
-    float* Tm = Ss + (size_t)HP * BM * BN;                         // [H][HP]: mix[h][g], zeros beyond g = H
+    float* Ss = reinterpret_cast<float*>(Vs + (size_t)KVH * BN * LV);   // [HP][SQ][BN], a thread's columns side by side
+    float* Tm = Ss + (size_t)HP * SQ * BN;                         // [H][HP]: mix[h][g], zeros beyond g = H
     long long* slot_s = reinterpret_cast<long long*>(Tm + (size_t)H * HP);   // [2][BN]
     const bool has_mix = p.mix != nullptr;
 
-    const int tile = blockIdx.x, split = blockIdx.y;
+    const int tile = gridDim.x - 1 - blockIdx.x, split = blockIdx.y;   // a prompt's last tiles see the most keys: they start first
     const int req = p.tile_req[tile];
     const int t0 = p.cu_q[req] + p.tile_tok0[tile];
     const int nq = min(BM, p.cu_q[req + 1] - t0);
@@ -127,13 +139,17 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
         }
         return (long long)page * p.page_size + j % p.page_size;
     };
-    // rows of all key/value heads for the BN keys whose slots are given: dst [KVH][BN][ld]
+    // rows of all key/value heads for the BN keys whose slots are given: dst [KVH][BN][ld]. A warp takes a key: its row of KVH * width
+    // entries is one run of memory.
     auto issue_rows = [&](bf16* dst, int ld, const bf16* pool, int width, const long long* slots) {
-        const int cpr = width / 8, per_key = KVH * cpr, total = BN * per_key;
-        for (int i = tid; i < total; i += nthreads) {
-            const int key = i / per_key, rem = i - key * per_key, kc = rem / cpr, ch = rem - kc * cpr;
+        const int shift = width == 128 ? 4 : 3, row_chunks = KVH << shift;   // 16-byte pieces per head row: 16 or 8
+        for (int key = warp; key < BN; key += n_warps) {
             const long long s = slots[key];
-            cp_async_16(dst + ((size_t)kc * BN + key) * ld + ch * 8, pool + (s < 0 ? 0 : s) * (long long)(KVH * width) + kc * width + ch * 8, s >= 0);
+            const bf16* src = pool + (s < 0 ? 0 : s) * (long long)(KVH * width);
+            for (int j = lane; j < row_chunks; j += 32) {
+                const int kc = j >> shift, ch = j & ((1 << shift) - 1);
+                cp_async_16(dst + ((size_t)kc * BN + key) * ld + ch * 8, src + j * 8, s >= 0);
+            }
         }
     };
 
@@ -152,7 +168,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
                 const int h = i / HP, g = i - h * HP;
                 Tm[i] = g < H ? p.mix[h * H + g] : 0.f;
             }
-            for (int i = tid; i < (HP - H) * BM * BN; i += nthreads) Ss[(size_t)H * BM * BN + i] = 0.f;
+            for (int i = tid; i < (HP - H) * SQ * BN; i += nthreads) Ss[(size_t)H * SQ * BN + i] = 0.f;
         }
         if (tid < BN) slot_s[tid] = b_begin < b_end ? slot_of(b_begin * BN + tid) : -1;
     }
@@ -164,7 +180,8 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-    const float inv_cap = p.cap > 0.f ? 1.f / p.cap : 0.f;
+    const float k2 = p.cap > 0.f ? 2.f * p.scale / p.cap * LOG2E : 0.f;
+    const int pos_min = pos0 + qt * R;   // the earliest position among this warp's queries
 
     for (int b = b_begin, it = 0; b < b_end; ++b, ++it) {
         const long long* cur = slot_s + (it & 1) * BN;
@@ -194,14 +211,12 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
             for (int i = 0; i < 2; ++i)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float v = s[i][e] * p.scale;
-                    if (p.cap > 0.f) v = p.cap * tanh_exp(v * inv_cap);
-                    s[i][e] = v;
+                    s[i][e] = p.cap > 0.f ? capped(s[i][e], k2, p.cap) : s[i][e] * p.scale;
                 }
             if (has_mix) {
                 // place (quad, n-tile, e) of a row <-> key column n-tile * 8 + 2 * quad + e
-                *reinterpret_cast<float4*>(Ss + ((size_t)h_a * BM + qq_a) * BN + quad * 4) = make_float4(s[0][0], s[0][1], s[1][0], s[1][1]);
-                *reinterpret_cast<float4*>(Ss + ((size_t)h_b * BM + qq_b) * BN + quad * 4) = make_float4(s[0][2], s[0][3], s[1][2], s[1][3]);
+                if (valid_a) *reinterpret_cast<float4*>(Ss + ((size_t)h_a * SQ + qq_a) * BN + quad * 4) = make_float4(s[0][0], s[0][1], s[1][0], s[1][1]);
+                if (valid_b) *reinterpret_cast<float4*>(Ss + ((size_t)h_b * SQ + qq_b) * BN + quad * 4) = make_float4(s[0][2], s[0][3], s[1][2], s[1][3]);
             }
         }
         __syncthreads();   // every head's scores are in shared memory; nobody reads this block's K any more
@@ -217,10 +232,11 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
                 for (int e = 0; e < 4; ++e) sp[0][e] = sp[1][e] = 0.f;
                 const float* Ta = Tm + (size_t)h_a * HP;
                 const float* Tb = Tm + (size_t)h_b * HP;
-                const float* Sa = Ss + (size_t)qq_a * BN + quad * 4;
-                const float* Sb = Ss + (size_t)qq_b * BN + quad * 4;
+                // rows of queries that the tile does not have are not exchanged: such a thread reads row 0 and its result is masked
+                const float* Sa = Ss + (size_t)(valid_a ? qq_a : 0) * BN + quad * 4;
+                const float* Sb = Ss + (size_t)(valid_b ? qq_b : 0) * BN + quad * 4;
                 const bool same_q = qq_a == qq_b;   // the same for the whole warp (R <= 8)
-                const size_t per_head = (size_t)BM * BN;
+                const size_t per_head = (size_t)SQ * BN;
                 for (int g0 = 0; g0 < HP; g0 += 4) {
                     const float4 ta = *reinterpret_cast<const float4*>(Ta + g0);
                     const float4 tb = *reinterpret_cast<const float4*>(Tb + g0);
@@ -239,36 +255,49 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
                 sp[0][0] = s[0][0]; sp[0][1] = s[0][1]; sp[0][2] = s[1][0]; sp[0][3] = s[1][1];
                 sp[1][0] = s[0][2]; sp[1][1] = s[0][3]; sp[1][2] = s[1][2]; sp[1][3] = s[1][3];
             }
-            // ---- mask, running maximum and sum
-            float mx_a = -INFINITY, mx_b = -INFINITY;
+            // ---- mask, running maximum and sum. A block that every row of the warp sees whole needs no mask (all but a tile's last
+            // block or two, and a window's first).
+            const bool whole = (qt + 1) * R <= nq && b * BN + BN - 1 <= pos_min && (p.window == 0 || b * BN > pos_min + R - 1 - p.window);
             bool see_a[4], see_b[4];
 #pragma unroll
+            for (int e = 0; e < 4; ++e) see_a[e] = see_b[e] = true;
+            if (!whole) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = b * BN + (e >> 1) * 8 + 2 * quad + (e & 1);
+                    see_a[e] = valid_a && j <= pos_a && j >= lo_a;
+                    see_b[e] = valid_b && j <= pos_b && j >= lo_b;
+                }
+            }
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int j = b * BN + (e >> 1) * 8 + 2 * quad + (e & 1);
-                see_a[e] = valid_a && j <= pos_a && j >= lo_a;
-                see_b[e] = valid_b && j <= pos_b && j >= lo_b;
                 if (see_a[e]) mx_a = fmaxf(mx_a, sp[0][e]);
                 if (see_b[e]) mx_b = fmaxf(mx_b, sp[1][e]);
             }
             mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
             mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
             const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-            const float corr_a = mn_a == -INFINITY ? 1.f : __expf(m_a - mn_a), corr_b = mn_b == -INFINITY ? 1.f : __expf(m_b - mn_b);
+            const bool moved = mn_a != m_a || mn_b != m_b;
+            const float corr_a = mn_a == -INFINITY ? 1.f : ex2_fast((m_a - mn_a) * LOG2E), corr_b = mn_b == -INFINITY ? 1.f : ex2_fast((m_b - mn_b) * LOG2E);
+            const float off_a = mn_a == -INFINITY ? 0.f : mn_a * LOG2E, off_b = mn_b == -INFINITY ? 0.f : mn_b * LOG2E;
             float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                sp[0][e] = see_a[e] ? __expf(sp[0][e] - mn_a) : 0.f;
-                sp[1][e] = see_b[e] ? __expf(sp[1][e] - mn_b) : 0.f;
+                sp[0][e] = see_a[e] ? ex2_fast(fmaf(sp[0][e], LOG2E, -off_a)) : 0.f;
+                sp[1][e] = see_b[e] ? ex2_fast(fmaf(sp[1][e], LOG2E, -off_b)) : 0.f;
                 sum_a += sp[0][e];
                 sum_b += sp[1][e];
             }
             m_a = mn_a; m_b = mn_b;
             l_a = l_a * corr_a + sum_a;   // this thread's share of the row's sum; the quad's shares meet at the end
             l_b = l_b * corr_b + sum_b;
+            if (__any_sync(0xffffffffu, moved)) {   // once the maxima have settled there is nothing to rescale
 #pragma unroll
-            for (int i = 0; i < DV / 8; ++i) {
-                o_acc[i][0] *= corr_a; o_acc[i][1] *= corr_a;
-                o_acc[i][2] *= corr_b; o_acc[i][3] *= corr_b;
+                for (int i = 0; i < DV / 8; ++i) {
+                    o_acc[i][0] *= corr_a; o_acc[i][1] *= corr_a;
+                    o_acc[i][2] *= corr_b; o_acc[i][3] *= corr_b;
+                }
             }
             pa[0] = pack_bf16(sp[0][0], sp[0][1]); pa[1] = pack_bf16(sp[1][0], sp[1][1]);
             pa[2] = pack_bf16(sp[0][2], sp[0][3]); pa[3] = pack_bf16(sp[1][2], sp[1][3]);
@@ -345,36 +374,33 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
     }
 }
 
-// One block per token: the pieces' maxima, sums and outputs become the row. grid = tokens.
+// One block per (token, head): the pieces' maxima, sums and outputs become the row. grid = (tokens, H), DV / 2 threads.
 __global__ void attn_mix_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, int H,
                                         int DV, int sink_one, const bf16* __restrict__ gate, int gate_stride) {
-    const int t = blockIdx.x, total = H * DV;
-    const float* ml = part_ml + (size_t)t * splits * H * 2;
-    const float* po = part_o + (size_t)t * splits * total;
-    for (int e = threadIdx.x * 2; e < total; e += blockDim.x * 2) {
-        const int h = e / DV;
-        float M = sink_one ? 0.f : -INFINITY;
-        for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[((size_t)s * H + h) * 2]);
-        float L = sink_one ? __expf(-M) : 0.f, x = 0.f, y = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = ml[((size_t)s * H + h) * 2];
-            if (m == -INFINITY) continue;
-            const float w = __expf(m - M);
-            L = fmaf(ml[((size_t)s * H + h) * 2 + 1], w, L);
-            const float2 o = *reinterpret_cast<const float2*>(po + (size_t)s * total + e);
-            x = fmaf(o.x, w, x);
-            y = fmaf(o.y, w, y);
-        }
-        const float f = L > 0.f ? 1.f / L : 0.f;
-        x *= f;
-        y *= f;
-        if (gate != nullptr) {
-            const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)t * gate_stride + e);
-            x = x / (1.f + __expf(-__low2float(g)));
-            y = y / (1.f + __expf(-__high2float(g)));
-        }
-        *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * total + e) = __floats2bfloat162_rn(x, y);
+    const int t = blockIdx.x, h = blockIdx.y, total = H * DV, e = h * DV + threadIdx.x * 2;
+    const float* ml = part_ml + ((size_t)t * splits * H + h) * 2;
+    const float* po = part_o + (size_t)t * splits * total + e;
+    float M = sink_one ? 0.f : -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, ml[(size_t)s * H * 2]);
+    float L = sink_one ? __expf(-M) : 0.f, x = 0.f, y = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) {
+        const float m = ml[(size_t)s * H * 2], l = ml[(size_t)s * H * 2 + 1];
+        const float2 o = *reinterpret_cast<const float2*>(po + (size_t)s * total);
+        const float w = m == -INFINITY ? 0.f : __expf(m - M);
+        L = fmaf(l, w, L);
+        x = fmaf(o.x, w, x);
+        y = fmaf(o.y, w, y);
     }
+    const float f = L > 0.f ? 1.f / L : 0.f;
+    x *= f;
+    y *= f;
+    if (gate != nullptr) {
+        const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)t * gate_stride + e);
+        x = x / (1.f + __expf(-__low2float(g)));
+        y = y / (1.f + __expf(-__high2float(g)));
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * total + e) = __floats2bfloat162_rn(x, y);
 }
 
 template <int DK, int DV>
@@ -391,26 +417,27 @@ int launch_mix_mma(const MixArgs& a, int n_tiles, size_t smem, cudaStream_t stre
 }   // namespace
 
 // Shared memory the tiled kernel needs for these sizes with `qt` query parts per block; 0 when it cannot take them at all.
-OXR_API long long oxr_attention_mix_mma_smem(int DK, int DV, int H, int KVH, int qt) {
+OXR_API long long oxr_attention_mix_mma_smem(int DK, int DV, int H, int KVH, int qt, int single) {
     if ((DK != 64 && DK != 128) || (DV != 64 && DV != 128) || H <= 0 || KVH <= 0 || H % KVH || qt <= 0) return 0;
     const int per = H / KVH;
     if (per > 16 || 16 % per || KVH * qt > MAX_WARPS) return 0;
-    return (long long)mix_smem_bytes(DK, DV, H, KVH, (H + 3) & ~3, qt);
+    return (long long)mix_smem_bytes(DK, DV, H, KVH, (H + 3) & ~3, qt, single ? 1 : qt * (16 / per));
 }
 
-OXR_API int oxr_attention_mix_mma(void* out, const void* q, int q_stride, const void* k_pool, const void* v_pool, int DK, int DV, int H, int KVH, int qt,
+// `single`: every tile is one token (a decode step); qt is then 1 and the score exchange keeps one row per head, so two blocks fit an SM.
+OXR_API int oxr_attention_mix_mma(void* out, const void* q, int q_stride, const void* k_pool, const void* v_pool, int DK, int DV, int H, int KVH, int qt, int single,
                                   const int* tile_req, const int* tile_tok0, int n_tiles, const int* cu_q, const int* positions, int n_tokens,
                                   const int* block_table, int table_width, int page_size, int num_pages, float scale, float cap, const float* mix,
                                   int sink_one, int window, const void* gate, int gate_stride, int splits, float* part_o, float* part_ml, int* status,
                                   cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return 0;
-    const long long smem = oxr_attention_mix_mma_smem(DK, DV, H, KVH, qt);
-    if (smem <= 0 || smem > 227 * 1024 || page_size <= 0 || window < 0 || cap < 0.f || splits < 1 || q_stride % 8 || gate_stride % 2 ||
+    const long long smem = oxr_attention_mix_mma_smem(DK, DV, H, KVH, qt, single);
+    if ((single && qt != 1) || smem <= 0 || smem > 227 * 1024 || page_size <= 0 || window < 0 || cap < 0.f || splits < 1 || q_stride % 8 || gate_stride % 2 ||
         (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
         return OXR_BAD_ARGUMENT;
     MixArgs a;
     a.out = (bf16*)out; a.q = (const bf16*)q; a.q_stride = q_stride; a.k_pool = (const bf16*)k_pool; a.v_pool = (const bf16*)v_pool;
-    a.H = H; a.KVH = KVH; a.HP = (H + 3) & ~3; a.QT = qt;
+    a.H = H; a.KVH = KVH; a.HP = (H + 3) & ~3; a.QT = qt; a.SQ = single ? 1 : qt * (16 / (H / KVH));
     a.tile_req = tile_req; a.tile_tok0 = tile_tok0; a.cu_q = cu_q; a.positions = positions;
     a.block_table = block_table; a.table_width = table_width; a.page_size = page_size; a.num_pages = num_pages;
     a.scale = scale; a.cap = cap; a.mix = mix; a.sink_one = sink_one; a.window = window;
@@ -421,6 +448,6 @@ OXR_API int oxr_attention_mix_mma(void* out, const void* q, int q_stride, const 
     else if (DV == 64) rc = launch_mix_mma<128, 64>(a, n_tiles, (size_t)smem, stream);
     else rc = launch_mix_mma<128, 128>(a, n_tiles, (size_t)smem, stream);
     if (rc != 0 || splits == 1) return rc;
-    attn_mix_combine_kernel<<<n_tokens, 256, 0, stream>>>((bf16*)out, part_o, part_ml, splits, H, DV, sink_one, (const bf16*)gate, gate_stride);
+    attn_mix_combine_kernel<<<dim3(n_tokens, H), DV / 2, 0, stream>>>((bf16*)out, part_o, part_ml, splits, H, DV, sink_one, (const bf16*)gate, gate_stride);
     return oxr_launch_status();
 }

@@ -277,26 +277,46 @@ OXR_API int oxr_rotary_angles(float* cos_out, float* sin_out, const int* positio
 // ---------------------------------------------------------------------------------------------- layer norm of the stream
 // out[r] = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight + bias for stream row `rows ? rows[r] : r`; the mean first,
 // then the mean of the squared deviations (two passes, not E[x^2] - E[x]^2), all in fp32. One block per output row.
+// The row is read once into shared memory (dynamic: hidden floats); the three passes run there.
+template <typename T>
+__device__ __forceinline__ void layer_norm_of_row(T* __restrict__ dst, const float* row, float sum, const float* __restrict__ weight,
+                                                  const float* __restrict__ bias, int hidden, float eps, float* red) {
+    const float mean = block_sum(sum, red) / (float)hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float d = row[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float b = bias != nullptr ? bias[i] : 0.f;
+        dst[i] = Num<T>::from_f32((row[i] - mean) * inv * weight[i] + b);
+    }
+}
+
 template <typename T>
 __global__ void stream_layer_norm_kernel(T* __restrict__ out, const float* __restrict__ stream, const float* __restrict__ weight,
                                          const float* __restrict__ bias, const int* __restrict__ rows, int hidden, float eps) {
+    extern __shared__ float ln_row[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* x = stream + (size_t)(rows ? rows[r] : r) * hidden;
     float s = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) s += x[i];
-    const float mean = block_sum(s, red) / (float)hidden;
-    float ss = 0.f;
+#pragma unroll 4
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float d = x[i] - mean;
-        ss = fmaf(d, d, ss);
+        const float v = x[i];
+        ln_row[i] = v;
+        s += v;
     }
-    const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
-    T* dst = out + (size_t)r * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float b = bias != nullptr ? bias[i] : 0.f;
-        dst[i] = Num<T>::from_f32((x[i] - mean) * inv * weight[i] + b);
-    }
+    layer_norm_of_row<T>(out + (size_t)r * hidden, ln_row, s, weight, bias, hidden, eps, red);
+}
+
+template <typename K>
+static int with_row_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    if (bytes > 200 * 1024) return OXR_BAD_ARGUMENT;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
 
 OXR_API int oxr_stream_layer_norm(void* out, const float* stream, const float* weight, const float* bias, const int* rows, int n_out, int hidden,
@@ -304,8 +324,14 @@ OXR_API int oxr_stream_layer_norm(void* out, const float* stream, const float* w
     if (n_out <= 0) return 0;
     if (hidden <= 0) return OXR_BAD_ARGUMENT;
     const int threads = hidden >= 1024 ? 256 : 128;
-    if (dtype == 0) stream_layer_norm_kernel<float><<<n_out, threads, 0, stream_>>>((float*)out, stream, weight, bias, rows, hidden, eps);
-    else stream_layer_norm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream_>>>((__nv_bfloat16*)out, stream, weight, bias, rows, hidden, eps);
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (dtype == 0) {
+        if (int rc = with_row_smem(stream_layer_norm_kernel<float>, smem)) return rc;
+        stream_layer_norm_kernel<float><<<n_out, threads, smem, stream_>>>((float*)out, stream, weight, bias, rows, hidden, eps);
+    } else {
+        if (int rc = with_row_smem(stream_layer_norm_kernel<__nv_bfloat16>, smem)) return rc;
+        stream_layer_norm_kernel<__nv_bfloat16><<<n_out, threads, smem, stream_>>>((__nv_bfloat16*)out, stream, weight, bias, rows, hidden, eps);
+    }
     return oxr_launch_status();
 }
 
@@ -319,36 +345,83 @@ OXR_API int oxr_stream_layer_norm(void* out, const float* stream, const float* w
 //
 // ab / fb: an optional fp32 bias row added to a / f before anything else (a sublayer's output bias).
 template <typename T>
+__device__ __forceinline__ float gated_residual_at(size_t i, size_t row, int c, float* __restrict__ stream, const T* __restrict__ a,
+                                                   const float* __restrict__ ab, const T* __restrict__ f, const float* __restrict__ fb,
+                                                   const T* __restrict__ gates, int gates_stride, const float* __restrict__ gate_bias,
+                                                   float* __restrict__ history, int index, const float* __restrict__ mixw, int hidden, size_t total) {
+    float y = Num<T>::to_f32(a[i]);
+    if (ab != nullptr) y += ab[c];
+    if (gates != nullptr) {
+        const float g = Num<T>::to_f32(gates[row * gates_stride + c]) + (gate_bias != nullptr ? gate_bias[c] : 0.f);
+        y = y / (1.f + expf(-g));
+    }
+    if (f != nullptr) {
+        float z = Num<T>::to_f32(f[i]);
+        if (fb != nullptr) z += fb[c];
+        if (gates != nullptr) {
+            const float g = Num<T>::to_f32(gates[row * gates_stride + hidden + c]) + (gate_bias != nullptr ? gate_bias[hidden + c] : 0.f);
+            z = z / (1.f + expf(-g));
+        }
+        y += z;
+    }
+    float x = stream[i] + y;
+    if (history != nullptr) {
+        history[(size_t)index * total + i] = x;
+        float acc = 0.f;
+        for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
+        x = fmaf(mixw[index], x, acc);
+    }
+    stream[i] = x;
+    return x;
+}
+
+template <typename T>
 __global__ void gated_residual_kernel(float* __restrict__ stream, const T* __restrict__ a, const float* __restrict__ ab, const T* __restrict__ f,
                                       const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride, const float* __restrict__ gate_bias,
                                       float* __restrict__ history, int index, const float* __restrict__ mixw, int hidden, size_t total) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t row = i / hidden;
-        const int c = (int)(i - row * hidden);
-        float y = Num<T>::to_f32(a[i]);
-        if (ab != nullptr) y += ab[c];
-        if (gates != nullptr) {
-            const float g = Num<T>::to_f32(gates[row * gates_stride + c]) + (gate_bias != nullptr ? gate_bias[c] : 0.f);
-            y = y / (1.f + expf(-g));
-        }
-        if (f != nullptr) {
-            float z = Num<T>::to_f32(f[i]);
-            if (fb != nullptr) z += fb[c];
-            if (gates != nullptr) {
-                const float g = Num<T>::to_f32(gates[row * gates_stride + hidden + c]) + (gate_bias != nullptr ? gate_bias[hidden + c] : 0.f);
-                z = z / (1.f + expf(-g));
-            }
-            y += z;
-        }
-        float x = stream[i] + y;
-        if (history != nullptr) {
-            history[(size_t)index * total + i] = x;
-            float acc = 0.f;
-            for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
-            x = fmaf(mixw[index], x, acc);
-        }
-        stream[i] = x;
+        gated_residual_at<T>(i, row, (int)(i - row * hidden), stream, a, ab, f, fb, gates, gates_stride, gate_bias, history, index, mixw, hidden, total);
     }
+}
+
+// The same, one block per row, and the row goes on through the layer norm that reads it next (weight, bias, eps): out = LN(new stream row).
+template <typename T>
+__global__ void gated_residual_norm_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ a, const float* __restrict__ ab,
+                                           const T* __restrict__ f, const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride,
+                                           const float* __restrict__ gate_bias, float* __restrict__ history, int index, const float* __restrict__ mixw,
+                                           int hidden, size_t total, const float* __restrict__ weight, const float* __restrict__ bias, float eps) {
+    extern __shared__ float ln_row[];
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    float s = 0.f;
+#pragma unroll 2
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float x = gated_residual_at<T>(row * hidden + c, row, c, stream, a, ab, f, fb, gates, gates_stride, gate_bias, history, index, mixw, hidden, total);
+        ln_row[c] = x;
+        s += x;
+    }
+    layer_norm_of_row<T>(out + row * hidden, ln_row, s, weight, bias, hidden, eps, red);
+}
+
+OXR_API int oxr_gated_residual_norm(void* out, float* stream, const void* a, const float* ab, const void* f, const float* fb, const void* gates,
+                                    int gates_stride, const float* gate_bias, float* history, int index, const float* mixw, int n, int hidden,
+                                    const float* weight, const float* bias, float eps, int dtype, cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    if (hidden <= 0 || a == nullptr || weight == nullptr || (history != nullptr && (mixw == nullptr || index < 0))) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n * hidden, smem = (size_t)hidden * sizeof(float);
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == 0) {
+        if (int rc = with_row_smem(gated_residual_norm_kernel<float>, smem)) return rc;
+        gated_residual_norm_kernel<float><<<n, threads, smem, stream_>>>((float*)out, stream, (const float*)a, ab, (const float*)f, fb, (const float*)gates,
+                                                                        gates_stride, gate_bias, history, index, mixw, hidden, total, weight, bias, eps);
+    } else {
+        typedef __nv_bfloat16 B;
+        if (int rc = with_row_smem(gated_residual_norm_kernel<B>, smem)) return rc;
+        gated_residual_norm_kernel<B><<<n, threads, smem, stream_>>>((B*)out, stream, (const B*)a, ab, (const B*)f, fb, (const B*)gates, gates_stride,
+                                                                    gate_bias, history, index, mixw, hidden, total, weight, bias, eps);
+    }
+    return oxr_launch_status();
 }
 
 OXR_API int oxr_gated_residual(float* stream, const void* a, const float* ab, const void* f, const float* fb, const void* gates, int gates_stride,

@@ -151,17 +151,18 @@ def _lib():
         lib.oxr_combine_rows.argtypes = [p, p, p, p, i, i, i, i, p]
         lib.oxr_stream_layer_norm.argtypes = [p, p, p, p, p, i, i, f, i, p]
         lib.oxr_gated_residual.argtypes = [p, p, p, p, p, p, i, p, p, i, p, i, i, i, p]
+        lib.oxr_gated_residual_norm.argtypes = [p, p, p, p, p, p, p, i, p, p, i, p, i, i, p, p, f, i, p]
         lib.oxr_gelu_tanh.argtypes = [p, p, ll, i, p]
         lib.oxr_add_inplace.argtypes = [p, p, ll, i, p]
         lib.oxr_add_inplace.restype = c_int
         lib.oxr_attention_mix_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, f, p, i, i, p, i, i, p, p]
         lib.oxr_bias_rope_store.argtypes = [p, i, i, i, i, i, p, p, p, i, p, p, ll, p, i, i, p, p]
-        lib.oxr_attention_mix_mma.argtypes = [p, p, i, p, p, i, i, i, i, i, p, p, i, p, p, i, p, i, i, i, f, f, p, i, i, p, i, i, p, p, p, p]
+        lib.oxr_attention_mix_mma.argtypes = [p, p, i, p, p, i, i, i, i, i, i, p, p, i, p, p, i, p, i, i, i, f, f, p, i, i, p, i, i, p, p, p, p]
         lib.oxr_attention_mix_mma.restype = c_int
-        lib.oxr_attention_mix_mma_smem.argtypes = [i, i, i, i, i]
+        lib.oxr_attention_mix_mma_smem.argtypes = [i, i, i, i, i, i]
         lib.oxr_attention_mix_mma_smem.restype = c_longlong
         lib.oxr_expert_clamped_glu.argtypes = [p, p, p, i, i, i, f, f, i, p]
-        for name in ("oxr_stream_layer_norm", "oxr_gated_residual", "oxr_gelu_tanh", "oxr_attention_mix_rows", "oxr_bias_rope_store",
+        for name in ("oxr_stream_layer_norm", "oxr_gated_residual", "oxr_gelu_tanh", "oxr_attention_mix_rows", "oxr_bias_rope_store", "oxr_gated_residual_norm",
                      "oxr_expert_clamped_glu"):
             getattr(lib, name).restype = c_int
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
@@ -1143,10 +1144,12 @@ def stream_layer_norm(stream: torch.Tensor, weight: torch.Tensor, bias: torch.Te
 
 def gated_residual(stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None = None, *, gates: torch.Tensor | None = None,
                    gate_bias: torch.Tensor | None = None, a_bias: torch.Tensor | None = None, f_bias: torch.Tensor | None = None,
-                   history: torch.Tensor | None = None, index: int = 0, weights: torch.Tensor | None = None) -> torch.Tensor:
+                   history: torch.Tensor | None = None, index: int = 0, weights: torch.Tensor | None = None,
+                   norm: tuple[torch.Tensor, torch.Tensor | None, float] | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
     """In place on the fp32 stream: ``X = stream + (a' + f')`` where ``a' = (a + a_bias) * sigmoid(gates[:, :hidden] + gate_bias[:hidden])`` and
     ``f'`` likewise with the second half of ``gates`` (no gates: the sublayers' outputs as they are; ``f`` None: one sublayer). With a
-    ``history [slots, tokens, hidden]`` (fp32) X is kept as ``history[index]`` and the stream becomes ``sum_{j <= index} weights[j] history[j]``."""
+    ``history [slots, tokens, hidden]`` (fp32) X is kept as ``history[index]`` and the stream becomes ``sum_{j <= index} weights[j] history[j]``. With ``norm = (weight, bias or None, eps)`` the same
+    kernel goes on to the layer norm that reads the new stream next and returns its output in ``out_dtype``; else returns None."""
     _need(stream, "stream", torch.float32)
     _need(a, "a")
     n, hidden = stream.shape
@@ -1166,6 +1169,18 @@ def gated_residual(stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None
         _need(weights, "weights", torch.float32)
         if history.shape[1:] != stream.shape or not 0 <= index < history.shape[0] or weights.numel() <= index:
             raise KernelError("gated_residual: the history does not fit")
+    if norm is not None:
+        weight, bias, eps = norm
+        _need(weight, "norm weight", torch.float32)
+        if bias is not None:
+            _need(bias, "norm bias", torch.float32)
+        if out_dtype != a.dtype:
+            raise KernelError("gated_residual: the norm's output has the sublayers' dtype")
+        out = torch.empty((n, hidden), dtype=out_dtype, device=stream.device)
+        _done(_lib().oxr_gated_residual_norm(out.data_ptr(), stream.data_ptr(), a.data_ptr(), _ptr(a_bias), _ptr(f), _ptr(f_bias), _ptr(gates), stride,
+                                             _ptr(gate_bias), _ptr(history), int(index), _ptr(weights), n, hidden, weight.data_ptr(), _ptr(bias),
+                                             float(eps), _dtype_code(a), _stream()), "gated_residual_norm")
+        return out
     _done(_lib().oxr_gated_residual(stream.data_ptr(), a.data_ptr(), _ptr(a_bias), _ptr(f), _ptr(f_bias), _ptr(gates), stride, _ptr(gate_bias),
                                     _ptr(history), int(index), _ptr(weights), n, hidden, _dtype_code(a), _stream()), "gated_residual")
     return stream
@@ -1276,22 +1291,24 @@ def attention_mix_tile(num_heads: int, num_kv_heads: int, key_dim: int, value_di
     return None
 
 
-def attention_mix_splits(n_tiles: int, kv_len_bound: int) -> int:
+def attention_mix_splits(n_tiles: int, kv_len_bound: int, blocks_per_sm: int = 1) -> int:
     """Pieces into which the tiled head-mixing kernel cuts every tile's keys: enough blocks for all SMs, at least four key blocks each."""
     if n_tiles <= 0:
         return 1
     most = max(1, -(-int(kv_len_bound) // MIX_TILE_KEYS) // 4)
-    return max(1, min(most, num_sms() // n_tiles, 64))
+    return max(1, min(most, blocks_per_sm * num_sms() // n_tiles, 64))
 
 
 def attention_mix_tiled(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, *, tile: tuple[int, int],
                         tiles: tuple[torch.Tensor, torch.Tensor, int], cu_q: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                         kv_len_bound: int, scale: float, softcap: float = 0.0, head_mix: torch.Tensor | None = None, unit_sink: bool = False,
-                        window: int = 0, gate: torch.Tensor | None = None, status: torch.Tensor, splits: int | None = None) -> torch.Tensor:
+                        window: int = 0, gate: torch.Tensor | None = None, status: torch.Tensor, splits: int | None = None,
+                        single_tokens: bool = False) -> torch.Tensor:
     """The function of :func:`attention_mix_rows` in bfloat16 on the tensor cores. ``tile`` is what :func:`attention_mix_tile` gave for
     the sizes; ``tiles = (tile_req, tile_tok0, count)`` cuts every request's new tokens into runs of ``tile[0]`` tokens (the batch builder's
     list for the spec ``(tile[0], 1, any)``); ``kv_len_bound`` bounds every request's context and, with the number of tiles, decides into
-    how many pieces the keys are cut (``splits`` overrides it). Scores, the mixing, the softmax weights and all sums are fp32; the weights
+    how many pieces the keys are cut (``splits`` overrides it). ``single_tokens``: every request brings one token (a decode step); the blocks are
+    then half as large and two share an SM. Scores, the mixing, the softmax weights and all sums are fp32; the weights
     are rounded to bfloat16 for the product with the values."""
     global launch_count
     _need(q, "q", torch.bfloat16)
@@ -1312,14 +1329,17 @@ def attention_mix_tiled(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v
             raise KernelError("attention_mix_tiled: the gate does not fit")
         gate_stride = gate.stride(0)
     tile_req, tile_tok0, n_tiles = tiles
+    if single_tokens and n != n_tiles:
+        raise KernelError("attention_mix_tiled: single tokens mean one tile per token")
     if splits is None:
-        splits = attention_mix_splits(n_tiles, kv_len_bound)
+        splits = attention_mix_splits(n_tiles, kv_len_bound, 2 if single_tokens else 1)
     out = torch.empty((n, H * DV), dtype=q.dtype, device=q.device)
     part_o = part_ml = None
     if splits > 1:
         part_o = torch.empty((n, splits, H * DV), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n, splits, H, 2), dtype=torch.float32, device=q.device)
-    _done(_lib().oxr_attention_mix_mma(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), DK, DV, H, KV, int(tile[1]),
+    _done(_lib().oxr_attention_mix_mma(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), DK, DV, H, KV,
+                                       1 if single_tokens else int(tile[1]), int(bool(single_tokens)),
                                        tile_req.data_ptr(), tile_tok0.data_ptr(), int(n_tiles), cu_q.data_ptr(), positions.data_ptr(), n,
                                        block_table.data_ptr(), block_table.shape[1], page_size, pages, float(scale), float(softcap), _ptr(head_mix),
                                        int(bool(unit_sink)), int(window), gate.data_ptr() if gate is not None else None, gate_stride, int(splits),

@@ -5,6 +5,7 @@ command to put under ``ncu``.
     python -m oxr_inference_b200.ops.microbench gemm --m 8 --n 24576 --k 4096
     python -m oxr_inference_b200.ops.microbench attention --batch 8 --q-len 1 --context 2048
     python -m oxr_inference_b200.ops.microbench attention --batch 1 --q-len 2048 --context 2048
+    python -m oxr_inference_b200.ops.microbench mixed-attention --batch 1 --q-len 2048 --context 2048
     python -m oxr_inference_b200.ops.microbench norm --rows 8 --hidden 4096
     python -m oxr_inference_b200.ops.microbench rope --tokens 2048
     OXR_B200_TIMELINE=1 python -m oxr_inference_b200.ops.microbench timeline --batch 8 --context 2048
@@ -174,6 +175,40 @@ def rope(args) -> dict:
             "GB/s": round(T * width * 2 * 2 / us / 1e3, 1)}
 
 
+def mixed_attention(args) -> dict:
+    """Head-mixing attention (capped scores, an H x H mix, a unit sink, an output gate) on the tensor cores: `--batch` requests bring
+    `--q-len` tokens each over `--context` keys."""
+    dev, bf = "cuda", torch.bfloat16
+    H, KV, D, P, B, Q, CTX = args.heads, args.kv_heads, args.head_dim, args.page_size, args.batch, args.q_len, args.context
+    tile = ops.attention_mix_tile(H, KV, D, D, bf)
+    if tile is None:
+        raise SystemExit("the tiled kernel does not take these sizes")
+    per_req = -(-CTX // P)
+    g = torch.Generator(device=dev).manual_seed(0)
+    k_pool = torch.randn(B * per_req, P, KV, D, generator=g, device=dev).to(bf)
+    v_pool = torch.randn(B * per_req, P, KV, D, generator=g, device=dev).to(bf)
+    proj = (torch.randn(B * Q, 2 * H * D, generator=g, device=dev) * 0.5).to(bf)   # q | gate
+    mix = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, generator=g, device=dev)).contiguous()
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    table = torch.arange(B * per_req, dtype=torch.int32, device=dev).view(B, per_req).contiguous()
+    tiles = (i32([r for r in range(B) for _ in range(0, Q, tile[0])]), i32([t for _ in range(B) for t in range(0, Q, tile[0])]), B * -(-Q // tile[0]))
+    pos = i32([CTX - Q + i for _ in range(B) for i in range(Q)])
+    status = ops.new_status(dev)
+    cu = i32(list(range(0, B * Q + 1, Q)))
+
+    def run(i):
+        ops.attention_mix_tiled(proj, H, k_pool, v_pool, tile=tile, tiles=tiles, cu_q=cu, positions=pos,
+                                block_table=table, kv_len_bound=CTX, scale=D ** -0.5, softcap=30.0, head_mix=mix, unit_sink=True, gate=proj[:, H * D:],
+                                status=status, single_tokens=Q == 1)
+
+    us = _time(run, args.reps)
+    ops.check_status(status)
+    pairs = B * sum(CTX - Q + i + 1 for i in range(Q))
+    return {"what": "mixed_attention", "batch": B, "q_len": Q, "context": CTX, "heads": H, "kv_heads": KV, "head_dim": D, "tile": tile,
+            "splits": ops.attention_mix_splits(tiles[2], CTX, 2 if Q == 1 else 1), "us": round(us, 1),
+            "tflop_s": round(pairs * (4 * H * D + 2 * H * H) / us / 1e6, 2), "kv_gb_s": round(B * CTX * KV * 2 * D * 2 / us / 1e3, 1)}
+
+
 def timeline(args) -> dict:
     import ctypes
 
@@ -284,6 +319,15 @@ def main() -> None:
     r.add_argument("--head-dim", type=int, default=128)
     r.add_argument("--page-size", type=int, default=16)
     r.set_defaults(run=rope)
+    m = sub.add_parser("mixed-attention")
+    m.add_argument("--batch", type=int, default=1)
+    m.add_argument("--q-len", type=int, default=2048)
+    m.add_argument("--context", type=int, default=2048)
+    m.add_argument("--heads", type=int, default=32)
+    m.add_argument("--kv-heads", type=int, default=8)
+    m.add_argument("--head-dim", type=int, default=128)
+    m.add_argument("--page-size", type=int, default=16)
+    m.set_defaults(run=mixed_attention)
     t = sub.add_parser("timeline", help="kernel by kernel through one decode step (needs OXR_B200_TIMELINE=1)")
     t.add_argument("--batch", type=int, default=8)
     t.add_argument("--context", type=int, default=2048)
@@ -296,7 +340,7 @@ def main() -> None:
     t.add_argument("--vocab", type=int, default=151936)
     t.add_argument("--page-size", type=int, default=16)
     t.set_defaults(run=timeline)
-    for p in (g, a, n, r):
+    for p in (g, a, n, r, m):
         p.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     torch.backends.cuda.matmul.allow_tf32 = False

@@ -124,10 +124,16 @@ class ParallelBlock(Part):
       instead of X. The history lives in the step's shared dictionary under ``history_key``.
 
     The stream is kept whole in fp32, as in ``sandwich_norm``: ``forward`` takes it in ``residual`` (the first block: in ``x``), updates it
-    in place and returns ``(None, stream)``. Gates, both adds, the history entry and the weighted sum are one kernel."""
+    in place and returns ``(None, stream)``. Gates, both adds, the history entry and the weighted sum are one kernel. When the next block
+    is of this arrangement too (``keeps_add_for``), the block hands its sublayers' results on unadded (a :class:`PendingParallelAdd`) and that
+    kernel also runs the next block's norm, whose input it has at hand."""
 
     supports_deferred = False
     accepts_deferred_input = False
+
+    def keeps_add_for(self, after) -> bool:
+        """Whether ``after`` (the block that runs next, or None) takes this block's add into its norm."""
+        return isinstance(after, ParallelBlock) and hasattr(after.mixer_norm, "after_gated_residual")
 
     def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward | None, feed_forward_norm: Norm | None, *, runtime: Runtime,
                  hidden_size: int, gated: bool = False, depth_states: int = 0, history_slots: int = 0, history_key: str = "depth_history"):
@@ -177,7 +183,12 @@ class ParallelBlock(Part):
             self.gate_bias = torch.cat([self.vectors[name + ".b"] for name in self.gates.outs]).contiguous()
 
     def forward(self, x, residual: torch.Tensor | None, ctx: StepContext, cache: LayerCache, defer_output: bool = False):
-        if residual is None:
+        h = None
+        if isinstance(x, PendingParallelAdd):
+            # the block before left its add to this block's norm: one kernel for both
+            stream = residual
+            h = x.apply(stream, then=self.mixer_norm)
+        elif residual is None:
             if isinstance(x, DeferredLinear):
                 x = x.materialize()
             if x.dtype != torch.float32:
@@ -195,7 +206,8 @@ class ParallelBlock(Part):
                 history = torch.empty((self.history_slots, *stream.shape), dtype=torch.float32, device=stream.device)
                 history[0].copy_(stream)
                 ctx.shared[self.history_key] = history
-        h = self.mixer_norm.stream_norm(stream)
+        if h is None:
+            h = self.mixer_norm.stream_norm(stream)
         a_bias = None
         if hasattr(self.mixer, "forward_parts"):
             a, a_bias = self.mixer.forward_parts(h, ctx, cache)
@@ -207,6 +219,24 @@ class ParallelBlock(Part):
         gates = self.gates(h) if self.gated else None
         if gates is not None and gates.dtype != a.dtype:
             gates = ops.cast(gates, a.dtype)
-        ops.gated_residual(stream, a, f, gates=gates, gate_bias=self.gate_bias, a_bias=a_bias, history=history, index=self.depth_states - 1,
-                           weights=self.vectors.get("dwa"))
+        pending = PendingParallelAdd(a, f, gates, self.gate_bias, a_bias, history, self.depth_states - 1, self.vectors.get("dwa"))
+        if defer_output:
+            return pending, stream
+        pending.apply(stream)
         return None, stream
+
+
+class PendingParallelAdd:
+    """A parallel block's sublayer results, gates and history entry, not yet added to the stream."""
+
+    def __init__(self, a, f, gates, gate_bias, a_bias, history, index, weights):
+        self.args = (a, f)
+        self.kwargs = dict(gates=gates, gate_bias=gate_bias, a_bias=a_bias, history=history, index=index, weights=weights)
+
+    def apply(self, stream: torch.Tensor, then=None):
+        """Add to the stream in place; with ``then`` (a norm that offers ``after_gated_residual``) return that norm's output of the new stream."""
+        a, f = self.args
+        if then is None:
+            ops.gated_residual(stream, a, f, **self.kwargs)
+            return None
+        return then.after_gated_residual(stream, a, f, **self.kwargs)

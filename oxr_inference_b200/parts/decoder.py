@@ -166,7 +166,9 @@ class DecoderModel:
                 residual = self.joints[entry.joint].forward(residual, first, entry.joint_arg, ctx)
             # a block may leave its last projection to the next block's norm, if both sides say that they can
             after = self.blocks[self.schedule[pos + 1].layer] if pos + 1 < len(self.schedule) else None
-            if getattr(block, "supports_deferred", False) and getattr(after, "accepts_deferred_input", False):
+            keeps_add = getattr(block, "keeps_add_for", None)
+            if (getattr(block, "supports_deferred", False) and getattr(after, "accepts_deferred_input", False)) or (
+                    keeps_add is not None and keeps_add(after) and self.schedule[pos + 1].joint is None):
                 x, residual = block.forward(x, residual, ctx, cache.layer_cache(pos, ctx), defer_output=True)
             else:
                 x, residual = block.forward(x, residual, ctx, cache.layer_cache(pos, ctx))

@@ -415,7 +415,7 @@ class MixedHeadAttention(Mixer):
             o = ops.attention_mix_tiled(proj, self.H, k_pool, v_pool, tile=self.tile, tiles=ctx.tiles[self.tile_specs()[0]], cu_q=ctx.cu_q,
                                         positions=ctx.positions, block_table=group.block_table, kv_len_bound=ctx.kv_len_bound, scale=self.scale,
                                         softcap=self.softcap, head_mix=self.talk, unit_sink=self.unit_sink, window=self.window, gate=gate,
-                                        status=ctx.status)
+                                        status=ctx.status, single_tokens=ctx.single_tokens)
             return self.out(o), (self.vectors["o.b"] if self.biases else None)
         o = ops.attention_mix_rows(proj, self.H, k_pool, v_pool, positions=ctx.positions, req_of_token=ctx.req_of_token,
                                    block_table=group.block_table, scale=self.scale, softcap=self.softcap, head_mix=self.talk,

@@ -95,3 +95,7 @@ class LayerNorm(Norm):
 
     def stream_rows(self, stream: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         return ops.stream_layer_norm(stream, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
+
+    def after_gated_residual(self, stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None, **gated) -> torch.Tensor:
+        """The gated add of a block's sublayers into the stream (``ops.gated_residual``) and this norm of the result, in one kernel."""
+        return ops.gated_residual(stream, a, f, norm=(self.weight, self.bias, self.eps), out_dtype=a.dtype, **gated)

@@ -122,7 +122,10 @@ def test_layer_results_one_by_one(tmp_path):
     for b, f in zip(blocks, originals):
         def wrapped(*a, _f=f, **k):
             out = _f(*a, **k)
-            got.append(out[1].clone())
+            after = out[1].clone()
+            if out[0] is not None:   # the add is left to the next block's norm: made here, on the copy
+                out[0].apply(after)
+            got.append(after)
             return out
         b.forward = wrapped
     rc = r.cache.open("r")
@@ -338,6 +341,16 @@ def plain_mixed_attention(q, k, v, pos, ctx_of, *, scale, cap, mix, sink, window
 @pytest.mark.parametrize("H,KV,DK,DV", [(8, 2, 64, 128), (4, 4, 128, 64), (16, 1, 64, 64), (6, 3, 128, 128), (32, 8, 128, 128), (2, 1, 64, 64)])
 @pytest.mark.parametrize("window,splits", [(0, None), (0, 3), (37, 1), (21, 2)])
 def test_tiled_kernel_against_the_formulas(H, KV, DK, DV, window, splits):
+    tiled_case(H, KV, DK, DV, window, splits, [1, 1, 67, 2, 45], False)
+
+
+@pytest.mark.parametrize("H,KV,DK,DV", [(8, 2, 64, 128), (32, 8, 128, 128), (3 * 2, 3, 64, 64), (16, 16, 128, 64)])
+@pytest.mark.parametrize("window,splits", [(0, None), (50, 4), (0, 9)])
+def test_tiled_kernel_on_single_tokens(H, KV, DK, DV, window, splits):
+    tiled_case(H, KV, DK, DV, window, splits, [1, 1, 1, 1, 1], True)
+
+
+def tiled_case(H, KV, DK, DV, window, splits, q_lens, single):
     """Requests of unequal lengths and portions (one token, two, a run that ends inside a tile, a long one) over pages dealt out in a
     shuffled order; the keys in one piece and in several; with and without a window; the mix far from the identity."""
     from oxr_inference_b200 import ops
@@ -345,7 +358,7 @@ def test_tiled_kernel_against_the_formulas(H, KV, DK, DV, window, splits):
     g = torch.Generator().manual_seed(H * 1000 + DK + window)
     tile = ops.attention_mix_tile(H, KV, DK, DV, torch.bfloat16)
     assert tile is not None
-    P, ctx_lens, q_lens = 8, [70, 1, 131, 19, 45], [1, 1, 67, 2, 45]
+    P, ctx_lens = 8, [70, 1, 131, 19, 45]
     n_pages = sum(-(-c // P) for c in ctx_lens) + 3
     order = torch.randperm(n_pages, generator=g).tolist()
     k_pool = torch.zeros(n_pages, P, KV, DK, dtype=torch.bfloat16)
@@ -381,7 +394,7 @@ def test_tiled_kernel_against_the_formulas(H, KV, DK, DV, window, splits):
     common = dict(positions=torch.cat(pos).to(DEV, torch.int32), block_table=table.to(DEV), scale=scale, softcap=cap, head_mix=mix.to(DEV),
                   unit_sink=True, window=window, gate=proj[:, H * DK + 24:], status=status)
     got = ops.attention_mix_tiled(proj, H, k_pool.to(DEV), v_pool.to(DEV), tile=tile, tiles=(i32(treq), i32(ttok), len(treq)), cu_q=cu,
-                                  kv_len_bound=max(ctx_lens), splits=splits, **common)
+                                  kv_len_bound=max(ctx_lens), splits=splits, single_tokens=single, **common)
     rows = ops.attention_mix_rows(proj, H, k_pool.to(DEV), v_pool.to(DEV), req_of_token=torch.repeat_interleave(torch.arange(len(q_lens)), torch.tensor(q_lens)).to(DEV, torch.int32),
                                   **common)
     ops.check_status(status)
