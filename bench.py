@@ -702,7 +702,7 @@ def vazepel_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         like = f"paged_attention {name} ({'cp.async mma' if prefill else 'cp.async split-KV'})"
         common = dict(positions=pos, block_table=table, scale=D ** -0.5, softcap=30.0, head_mix=mix, unit_sink=True, gate=proj[:, cq + ck + cv:], status=status)
         ms = _time_ms(lambda: ops.attention_mix_tiled(proj, H, k_pool, v_pool, tile=tile, tiles=tiles_for((tile[0], 1, 1 << 30)), cu_q=cu,
-                                                      kv_len_bound=max(ctx_lens), **common), flush=flush)
+                                                      kv_len_bound=max(ctx_lens), single_tokens=not prefill, **common), flush=flush)
         pairs = T * (T + 1) // 2 if prefill else sum(ctx_lens)
         if prefill:
             # q k and p v on the tensor cores, and the H x H mix of every (query, key) place on the fp32 pipes
@@ -726,6 +726,10 @@ def vazepel_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         ms = _time_ms(lambda: ops.gated_residual(stream, a, f_, gates=gates, gate_bias=gb, a_bias=ab, history=history, index=depth, weights=dw), flush=flush)
         put(f"gated_residual {name} (two gates, both adds, history of {depth + 1}, weighted sum)", f"add_rms_norm {name}", ms,
             bytes_=n * width * (4 + 2 + 2 + 4 + 4 + depth * 4 + 4))
+        ms = _time_ms(lambda: ops.gated_residual(stream, a, f_, gates=gates, gate_bias=gb, a_bias=ab, history=history, index=depth, weights=dw,
+                                                 norm=(w, b, 1e-5), out_dtype=bf), flush=flush)
+        put(f"gated_residual + layer norm {name} (one kernel: what runs between two blocks)", f"add_rms_norm {name}", ms,
+            bytes_=n * width * (4 + 2 + 2 + 4 + 4 + depth * 4 + 4 + 2))
         # ---- feed-forward activations
         gu = rand(n, 2 * ff)
         ms = _time_ms(lambda: ops.silu_mul(gu), flush=flush)

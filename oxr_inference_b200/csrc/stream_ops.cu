@@ -277,7 +277,17 @@ OXR_API int oxr_rotary_angles(float* cos_out, float* sin_out, const int* positio
 // ---------------------------------------------------------------------------------------------- layer norm of the stream
 // out[r] = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight + bias for stream row `rows ? rows[r] : r`; the mean first,
 // then the mean of the squared deviations (two passes, not E[x^2] - E[x]^2), all in fp32. One block per output row.
-// The row is read once into shared memory (dynamic: hidden floats); the three passes run there.
+// The row is read once into shared memory (dynamic: hidden floats); the three passes run there. Rows of a multiple of four entries
+// move as 16-byte pieces.
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = u;
+}
+
 template <typename T>
 __device__ __forceinline__ void layer_norm_of_row(T* __restrict__ dst, const float* row, float sum, const float* __restrict__ weight,
                                                   const float* __restrict__ bias, int hidden, float eps, float* red) {
@@ -288,25 +298,51 @@ __device__ __forceinline__ void layer_norm_of_row(T* __restrict__ dst, const flo
         ss = fmaf(d, d, ss);
     }
     const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    if ((hidden & 3) == 0) {
+        for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+            const float4 x = reinterpret_cast<const float4*>(row)[i], w = reinterpret_cast<const float4*>(weight)[i];
+            const float4 b = bias != nullptr ? reinterpret_cast<const float4*>(bias)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            store4(dst + 4 * i, make_float4((x.x - mean) * inv * w.x + b.x, (x.y - mean) * inv * w.y + b.y, (x.z - mean) * inv * w.z + b.z,
+                                            (x.w - mean) * inv * w.w + b.w));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         const float b = bias != nullptr ? bias[i] : 0.f;
         dst[i] = Num<T>::from_f32((row[i] - mean) * inv * weight[i] + b);
     }
 }
 
+// The norm's weight and bias are wanted only after two block-wide sums: asked for early, they are in L2 by then.
+__device__ __forceinline__ void prefetch_row(const float* p, int hidden) {
+    if (p == nullptr) return;
+    for (int i = threadIdx.x * 32; i < hidden; i += blockDim.x * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + i));
+}
+
 template <typename T>
 __global__ void stream_layer_norm_kernel(T* __restrict__ out, const float* __restrict__ stream, const float* __restrict__ weight,
                                          const float* __restrict__ bias, const int* __restrict__ rows, int hidden, float eps) {
-    extern __shared__ float ln_row[];
+    extern __shared__ __align__(16) float ln_row[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* x = stream + (size_t)(rows ? rows[r] : r) * hidden;
+    prefetch_row(weight, hidden);
+    prefetch_row(bias, hidden);
     float s = 0.f;
+    if ((hidden & 3) == 0) {
 #pragma unroll 4
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = x[i];
-        ln_row[i] = v;
-        s += v;
+        for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(x)[i];
+            reinterpret_cast<float4*>(ln_row)[i] = v;
+            s += (v.x + v.y) + (v.z + v.w);
+        }
+    } else {
+#pragma unroll 4
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = x[i];
+            ln_row[i] = v;
+            s += v;
+        }
     }
     layer_norm_of_row<T>(out + (size_t)r * hidden, ln_row, s, weight, bias, hidden, eps, red);
 }
@@ -391,11 +427,13 @@ __global__ void gated_residual_norm_kernel(T* __restrict__ out, float* __restric
                                            const T* __restrict__ f, const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride,
                                            const float* __restrict__ gate_bias, float* __restrict__ history, int index, const float* __restrict__ mixw,
                                            int hidden, size_t total, const float* __restrict__ weight, const float* __restrict__ bias, float eps) {
-    extern __shared__ float ln_row[];
+    extern __shared__ __align__(16) float ln_row[];
     __shared__ float red[32];
     const size_t row = blockIdx.x;
+    prefetch_row(weight, hidden);
+    prefetch_row(bias, hidden);
     float s = 0.f;
-#pragma unroll 2
+#pragma unroll 4
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const float x = gated_residual_at<T>(row * hidden + c, row, c, stream, a, ab, f, fb, gates, gates_stride, gate_bias, history, index, mixw, hidden, total);
         ln_row[c] = x;
