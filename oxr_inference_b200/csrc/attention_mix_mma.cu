@@ -171,6 +171,18 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
             for (int i = tid; i < (HP - H) * SQ * BN; i += nthreads) Ss[(size_t)H * SQ * BN + i] = 0.f;
         }
         if (tid < BN) slot_s[tid] = b_begin < b_end ? slot_of(b_begin * BN + tid) : -1;
+        // A piece of the keys (few tiles, the GPU is not full: every wait for memory shows): ask for all of the piece's K and V rows
+        // at once, so that the block-by-block copies find them in L2.
+        if (p.splits > 1 && b_end - b_begin <= 32) {
+            const int k_lines = KVH * DK * 2 / 128, v_lines = KVH * DV * 2 / 128, lines = k_lines + v_lines;
+            for (int i = tid; i < (b_end - b_begin) * BN * lines; i += nthreads) {
+                const int key = i / lines, line = i - key * lines;
+                const long long sl = slot_of(b_begin * BN + key);
+                if (sl < 0) continue;
+                const bf16* at = line < k_lines ? p.k_pool + sl * (long long)(KVH * DK) + line * 64 : p.v_pool + sl * (long long)(KVH * DV) + (line - k_lines) * 64;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(at));
+            }
+        }
     }
     __syncthreads();
     if (b_begin < b_end) issue_rows(Ks, LQ, p.k_pool, DK, slot_s);

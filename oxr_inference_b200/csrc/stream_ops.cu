@@ -380,11 +380,11 @@ OXR_API int oxr_stream_layer_norm(void* out, const float* stream, const float* w
 //   stream = sum_{j < index} mixw[j] * history[j] + mixw[index] * X       (the sum in the order of j), else stream = X.
 //
 // ab / fb: an optional fp32 bias row added to a / f before anything else (a sublayer's output bias).
+// What the sublayers add at place i = (row, c): the gated sum y, read-only.
 template <typename T>
-__device__ __forceinline__ float gated_residual_at(size_t i, size_t row, int c, float* __restrict__ stream, const T* __restrict__ a,
-                                                   const float* __restrict__ ab, const T* __restrict__ f, const float* __restrict__ fb,
-                                                   const T* __restrict__ gates, int gates_stride, const float* __restrict__ gate_bias,
-                                                   float* __restrict__ history, int index, const float* __restrict__ mixw, int hidden, size_t total) {
+__device__ __forceinline__ float gated_sum_at(size_t i, size_t row, int c, const T* __restrict__ a, const float* __restrict__ ab,
+                                              const T* __restrict__ f, const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride,
+                                              const float* __restrict__ gate_bias, int hidden) {
     float y = Num<T>::to_f32(a[i]);
     if (ab != nullptr) y += ab[c];
     if (gates != nullptr) {
@@ -400,15 +400,7 @@ __device__ __forceinline__ float gated_residual_at(size_t i, size_t row, int c, 
         }
         y += z;
     }
-    float x = stream[i] + y;
-    if (history != nullptr) {
-        history[(size_t)index * total + i] = x;
-        float acc = 0.f;
-        for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
-        x = fmaf(mixw[index], x, acc);
-    }
-    stream[i] = x;
-    return x;
+    return y;
 }
 
 template <typename T>
@@ -417,27 +409,50 @@ __global__ void gated_residual_kernel(float* __restrict__ stream, const T* __res
                                       float* __restrict__ history, int index, const float* __restrict__ mixw, int hidden, size_t total) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t row = i / hidden;
-        gated_residual_at<T>(i, row, (int)(i - row * hidden), stream, a, ab, f, fb, gates, gates_stride, gate_bias, history, index, mixw, hidden, total);
+        float x = stream[i] + gated_sum_at<T>(i, row, (int)(i - row * hidden), a, ab, f, fb, gates, gates_stride, gate_bias, hidden);
+        if (history != nullptr) {
+            history[(size_t)index * total + i] = x;
+            float acc = 0.f;
+            for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
+            x = fmaf(mixw[index], x, acc);
+        }
+        stream[i] = x;
     }
 }
 
 // The same, one block per row, and the row goes on through the layer norm that reads it next (weight, bias, eps): out = LN(new stream row).
+// Two passes: the first only reads global memory (the new row X and the weighted sum go to shared memory), so that its loads run ahead
+// of each other; the second writes X to the history and the sum to the stream. Shared memory: 2 * hidden floats.
 template <typename T>
-__global__ void gated_residual_norm_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ a, const float* __restrict__ ab,
+__global__ void gated_residual_norm_kernel(T* __restrict__ out, float* stream, const T* __restrict__ a, const float* __restrict__ ab,
                                            const T* __restrict__ f, const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride,
-                                           const float* __restrict__ gate_bias, float* __restrict__ history, int index, const float* __restrict__ mixw,
+                                           const float* __restrict__ gate_bias, float* history, int index, const float* __restrict__ mixw,
                                            int hidden, size_t total, const float* __restrict__ weight, const float* __restrict__ bias, float eps) {
-    extern __shared__ __align__(16) float ln_row[];
+    extern __shared__ __align__(16) float ln_row[];   // [hidden] the stream's new row, then [hidden] X
     __shared__ float red[32];
+    float* x_row = ln_row + hidden;
     const size_t row = blockIdx.x;
     prefetch_row(weight, hidden);
     prefetch_row(bias, hidden);
     float s = 0.f;
 #pragma unroll 4
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float x = gated_residual_at<T>(row * hidden + c, row, c, stream, a, ab, f, fb, gates, gates_stride, gate_bias, history, index, mixw, hidden, total);
+        const size_t i = row * hidden + c;
+        float x = stream[i] + gated_sum_at<T>(i, row, c, a, ab, f, fb, gates, gates_stride, gate_bias, hidden);
+        x_row[c] = x;
+        if (history != nullptr) {
+            float acc = 0.f;
+            for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
+            x = fmaf(mixw[index], x, acc);
+        }
         ln_row[c] = x;
         s += x;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const size_t i = row * hidden + c;
+        if (history != nullptr) history[(size_t)index * total + i] = x_row[c];
+        stream[i] = ln_row[c];
     }
     layer_norm_of_row<T>(out + row * hidden, ln_row, s, weight, bias, hidden, eps, red);
 }
@@ -447,7 +462,7 @@ OXR_API int oxr_gated_residual_norm(void* out, float* stream, const void* a, con
                                     const float* weight, const float* bias, float eps, int dtype, cudaStream_t stream_) {
     if (n <= 0) return 0;
     if (hidden <= 0 || a == nullptr || weight == nullptr || (history != nullptr && (mixw == nullptr || index < 0))) return OXR_BAD_ARGUMENT;
-    const size_t total = (size_t)n * hidden, smem = (size_t)hidden * sizeof(float);
+    const size_t total = (size_t)n * hidden, smem = 2 * (size_t)hidden * sizeof(float);
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == 0) {
         if (int rc = with_row_smem(gated_residual_norm_kernel<float>, smem)) return rc;
