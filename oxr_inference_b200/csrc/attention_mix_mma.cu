@@ -57,6 +57,12 @@ __device__ __forceinline__ float rcp_fast(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// a 16-byte word from shared memory by its 32-bit address: no generic-pointer arithmetic in the mixing loop
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
 constexpr float LOG2E = 1.4426950408889634f;
 // cap * tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1), with x = raw * scale and k2 = 2 * scale / cap * log2(e): absolute error of
 // a few 1e-7 of cap everywhere, exact limits at both ends (exp = inf: cap; exp = 0: -cap)
@@ -242,25 +248,22 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
             if (has_mix) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) sp[0][e] = sp[1][e] = 0.f;
-                const float* Ta = Tm + (size_t)h_a * HP;
-                const float* Tb = Tm + (size_t)h_b * HP;
                 // rows of queries that the tile does not have are not exchanged: such a thread reads row 0 and its result is masked
-                const float* Sa = Ss + (size_t)(valid_a ? qq_a : 0) * BN + quad * 4;
-                const float* Sb = Ss + (size_t)(valid_b ? qq_b : 0) * BN + quad * 4;
+                uint32_t ta = smem_u32(Tm + (size_t)h_a * HP), tb = smem_u32(Tm + (size_t)h_b * HP);
+                uint32_t sa = smem_u32(Ss + (size_t)(valid_a ? qq_a : 0) * BN + quad * 4), sb = smem_u32(Ss + (size_t)(valid_b ? qq_b : 0) * BN + quad * 4);
                 const bool same_q = qq_a == qq_b;   // the same for the whole warp (R <= 8)
-                const size_t per_head = (size_t)SQ * BN;
-                for (int g0 = 0; g0 < HP; g0 += 4) {
-                    const float4 ta = *reinterpret_cast<const float4*>(Ta + g0);
-                    const float4 tb = *reinterpret_cast<const float4*>(Tb + g0);
-                    const float tav[4] = {ta.x, ta.y, ta.z, ta.w}, tbv[4] = {tb.x, tb.y, tb.z, tb.w};
+                const uint32_t per_head = (uint32_t)(SQ * BN * sizeof(float));
+                for (int g0 = 0; g0 < HP; g0 += 4, ta += 16, tb += 16) {
+                    const float4 ta4 = lds128(ta), tb4 = lds128(tb);
+                    const float tav[4] = {ta4.x, ta4.y, ta4.z, ta4.w}, tbv[4] = {tb4.x, tb4.y, tb4.z, tb4.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float4 sa = *reinterpret_cast<const float4*>(Sa + (g0 + e) * per_head);
-                        const float4 sb = same_q ? sa : *reinterpret_cast<const float4*>(Sb + (g0 + e) * per_head);
-                        sp[0][0] = fmaf(tav[e], sa.x, sp[0][0]); sp[0][1] = fmaf(tav[e], sa.y, sp[0][1]);
-                        sp[0][2] = fmaf(tav[e], sa.z, sp[0][2]); sp[0][3] = fmaf(tav[e], sa.w, sp[0][3]);
-                        sp[1][0] = fmaf(tbv[e], sb.x, sp[1][0]); sp[1][1] = fmaf(tbv[e], sb.y, sp[1][1]);
-                        sp[1][2] = fmaf(tbv[e], sb.z, sp[1][2]); sp[1][3] = fmaf(tbv[e], sb.w, sp[1][3]);
+                    for (int e = 0; e < 4; ++e, sa += per_head, sb += per_head) {
+                        const float4 sav = lds128(sa);
+                        const float4 sbv = same_q ? sav : lds128(sb);
+                        sp[0][0] = fmaf(tav[e], sav.x, sp[0][0]); sp[0][1] = fmaf(tav[e], sav.y, sp[0][1]);
+                        sp[0][2] = fmaf(tav[e], sav.z, sp[0][2]); sp[0][3] = fmaf(tav[e], sav.w, sp[0][3]);
+                        sp[1][0] = fmaf(tbv[e], sbv.x, sp[1][0]); sp[1][1] = fmaf(tbv[e], sbv.y, sp[1][1]);
+                        sp[1][2] = fmaf(tbv[e], sbv.z, sp[1][2]); sp[1][3] = fmaf(tbv[e], sbv.w, sp[1][3]);
                     }
                 }
             } else {

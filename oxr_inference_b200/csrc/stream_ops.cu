@@ -403,6 +403,27 @@ __device__ __forceinline__ float gated_sum_at(size_t i, size_t row, int c, const
     return y;
 }
 
+// A load that the compiler knows to be from global memory: it need not wait for the stores to shared memory before it.
+__device__ __forceinline__ float global_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+// sum_{j < index} mixw[j] * history[j][i], added in the order of j; eight loads are asked for before the first is used
+__device__ __forceinline__ float history_sum(const float* history, const float* __restrict__ mixw, int index, size_t total, size_t i) {
+    float acc = 0.f;
+    for (int j0 = 0; j0 < index; j0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = j0 + u < index ? global_f32(history + (size_t)(j0 + u) * total + i) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (j0 + u < index) acc = fmaf(mixw[j0 + u], v[u], acc);
+    }
+    return acc;
+}
+
 template <typename T>
 __global__ void gated_residual_kernel(float* __restrict__ stream, const T* __restrict__ a, const float* __restrict__ ab, const T* __restrict__ f,
                                       const float* __restrict__ fb, const T* __restrict__ gates, int gates_stride, const float* __restrict__ gate_bias,
@@ -435,15 +456,13 @@ __global__ void gated_residual_norm_kernel(T* __restrict__ out, float* stream, c
     prefetch_row(weight, hidden);
     prefetch_row(bias, hidden);
     float s = 0.f;
-#pragma unroll 4
+#pragma unroll 2
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         const size_t i = row * hidden + c;
-        float x = stream[i] + gated_sum_at<T>(i, row, c, a, ab, f, fb, gates, gates_stride, gate_bias, hidden);
+        float x = global_f32(stream + i) + gated_sum_at<T>(i, row, c, a, ab, f, fb, gates, gates_stride, gate_bias, hidden);
         x_row[c] = x;
         if (history != nullptr) {
-            float acc = 0.f;
-            for (int j = 0; j < index; ++j) acc = fmaf(mixw[j], history[(size_t)j * total + i], acc);
-            x = fmaf(mixw[index], x, acc);
+            x = fmaf(mixw[index], x, history_sum(history, mixw, index, total, i));
         }
         ln_row[c] = x;
         s += x;
@@ -463,7 +482,7 @@ OXR_API int oxr_gated_residual_norm(void* out, float* stream, const void* a, con
     if (n <= 0) return 0;
     if (hidden <= 0 || a == nullptr || weight == nullptr || (history != nullptr && (mixw == nullptr || index < 0))) return OXR_BAD_ARGUMENT;
     const size_t total = (size_t)n * hidden, smem = 2 * (size_t)hidden * sizeof(float);
-    const int threads = hidden >= 1024 ? 256 : 128;
+    const int threads = hidden >= 4096 ? 1024 : hidden >= 2048 ? 512 : hidden >= 1024 ? 256 : 128;   // every thread's loads of a row are in flight together
     if (dtype == 0) {
         if (int rc = with_row_smem(gated_residual_norm_kernel<float>, smem)) return rc;
         gated_residual_norm_kernel<float><<<n, threads, smem, stream_>>>((float*)out, stream, (const float*)a, ab, (const float*)f, fb, (const float*)gates,

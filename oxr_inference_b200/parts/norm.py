@@ -97,5 +97,12 @@ class LayerNorm(Norm):
         return ops.stream_layer_norm(stream, self.weight, self.bias, self.eps, self.runtime.dtype, rows=rows)
 
     def after_gated_residual(self, stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None, **gated) -> torch.Tensor:
-        """The gated add of a block's sublayers into the stream (``ops.gated_residual``) and this norm of the result, in one kernel."""
+        """The gated add of a block's sublayers into the stream (``ops.gated_residual``) and this norm of the result: one kernel with a block
+        per row for up to ``FUSED_ROWS`` rows (decode steps and short portions, where a launch and a second pass over the row count), the
+        element-wise kernel and then the norm beyond (a prompt's 2,048 rows of 4,096: 95 + 24 us against 267 us in one kernel)."""
+        if stream.shape[0] > self.FUSED_ROWS:
+            ops.gated_residual(stream, a, f, **gated)
+            return self.stream_norm(stream)
         return ops.gated_residual(stream, a, f, norm=(self.weight, self.bias, self.eps), out_dtype=a.dtype, **gated)
+
+    FUSED_ROWS = 256
