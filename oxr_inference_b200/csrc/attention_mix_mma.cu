@@ -253,17 +253,31 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, 1) attn_mix_mma_kernel(const M
                 uint32_t sa = smem_u32(Ss + (size_t)(valid_a ? qq_a : 0) * BN + quad * 4), sb = smem_u32(Ss + (size_t)(valid_b ? qq_b : 0) * BN + quad * 4);
                 const bool same_q = qq_a == qq_b;   // the same for the whole warp (R <= 8)
                 const uint32_t per_head = (uint32_t)(SQ * BN * sizeof(float));
-                for (int g0 = 0; g0 < HP; g0 += 4, ta += 16, tb += 16) {
-                    const float4 ta4 = lds128(ta), tb4 = lds128(tb);
-                    const float tav[4] = {ta4.x, ta4.y, ta4.z, ta4.w}, tbv[4] = {tb4.x, tb4.y, tb4.z, tb4.w};
+                if (same_q) {   // both rows are the same query's: one word of scores serves both
+                    for (int g0 = 0; g0 < HP; g0 += 4, ta += 16, tb += 16) {
+                        const float4 ta4 = lds128(ta), tb4 = lds128(tb);
+                        const float tav[4] = {ta4.x, ta4.y, ta4.z, ta4.w}, tbv[4] = {tb4.x, tb4.y, tb4.z, tb4.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e, sa += per_head, sb += per_head) {
-                        const float4 sav = lds128(sa);
-                        const float4 sbv = same_q ? sav : lds128(sb);
-                        sp[0][0] = fmaf(tav[e], sav.x, sp[0][0]); sp[0][1] = fmaf(tav[e], sav.y, sp[0][1]);
-                        sp[0][2] = fmaf(tav[e], sav.z, sp[0][2]); sp[0][3] = fmaf(tav[e], sav.w, sp[0][3]);
-                        sp[1][0] = fmaf(tbv[e], sbv.x, sp[1][0]); sp[1][1] = fmaf(tbv[e], sbv.y, sp[1][1]);
-                        sp[1][2] = fmaf(tbv[e], sbv.z, sp[1][2]); sp[1][3] = fmaf(tbv[e], sbv.w, sp[1][3]);
+                        for (int e = 0; e < 4; ++e, sa += per_head) {
+                            const float4 sv = lds128(sa);
+                            sp[0][0] = fmaf(tav[e], sv.x, sp[0][0]); sp[0][1] = fmaf(tav[e], sv.y, sp[0][1]);
+                            sp[0][2] = fmaf(tav[e], sv.z, sp[0][2]); sp[0][3] = fmaf(tav[e], sv.w, sp[0][3]);
+                            sp[1][0] = fmaf(tbv[e], sv.x, sp[1][0]); sp[1][1] = fmaf(tbv[e], sv.y, sp[1][1]);
+                            sp[1][2] = fmaf(tbv[e], sv.z, sp[1][2]); sp[1][3] = fmaf(tbv[e], sv.w, sp[1][3]);
+                        }
+                    }
+                } else {
+                    for (int g0 = 0; g0 < HP; g0 += 4, ta += 16, tb += 16) {
+                        const float4 ta4 = lds128(ta), tb4 = lds128(tb);
+                        const float tav[4] = {ta4.x, ta4.y, ta4.z, ta4.w}, tbv[4] = {tb4.x, tb4.y, tb4.z, tb4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e, sa += per_head, sb += per_head) {
+                            const float4 sav = lds128(sa), sbv = lds128(sb);
+                            sp[0][0] = fmaf(tav[e], sav.x, sp[0][0]); sp[0][1] = fmaf(tav[e], sav.y, sp[0][1]);
+                            sp[0][2] = fmaf(tav[e], sav.z, sp[0][2]); sp[0][3] = fmaf(tav[e], sav.w, sp[0][3]);
+                            sp[1][0] = fmaf(tbv[e], sbv.x, sp[1][0]); sp[1][1] = fmaf(tbv[e], sbv.y, sp[1][1]);
+                            sp[1][2] = fmaf(tbv[e], sbv.z, sp[1][2]); sp[1][3] = fmaf(tbv[e], sbv.w, sp[1][3]);
+                        }
                     }
                 }
             } else {
