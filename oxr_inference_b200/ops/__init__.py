@@ -1145,11 +1145,11 @@ def stream_layer_norm(stream: torch.Tensor, weight: torch.Tensor, bias: torch.Te
 def gated_residual(stream: torch.Tensor, a: torch.Tensor, f: torch.Tensor | None = None, *, gates: torch.Tensor | None = None,
                    gate_bias: torch.Tensor | None = None, a_bias: torch.Tensor | None = None, f_bias: torch.Tensor | None = None,
                    history: torch.Tensor | None = None, index: int = 0, weights: torch.Tensor | None = None,
-                   norm: tuple[torch.Tensor, torch.Tensor | None, float] | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+                   norm: tuple[torch.Tensor, torch.Tensor | None, float] | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """In place on the fp32 stream: ``X = stream + (a' + f')`` where ``a' = (a + a_bias) * sigmoid(gates[:, :hidden] + gate_bias[:hidden])`` and
     ``f'`` likewise with the second half of ``gates`` (no gates: the sublayers' outputs as they are; ``f`` None: one sublayer). With a
     ``history [slots, tokens, hidden]`` (fp32) X is kept as ``history[index]`` and the stream becomes ``sum_{j <= index} weights[j] history[j]``. With ``norm = (weight, bias or None, eps)`` the same
-    kernel goes on to the layer norm that reads the new stream next and returns its output in ``out_dtype``; else returns None."""
+    kernel goes on to the layer norm that reads the new stream next and returns its output in ``out_dtype``; else returns the stream."""
     _need(stream, "stream", torch.float32)
     _need(a, "a")
     n, hidden = stream.shape

@@ -403,3 +403,48 @@ def tiled_case(H, KV, DK, DV, window, splits, q_lens, single):
     err_rows = (rows.float().cpu() - want).abs().max() / want.abs().max()
     assert err_rows < 1e-2, f"the rows kernel is off by {err_rows:.2e}"
     assert err < 1.5e-2, f"the tiled kernel is off by {err:.2e} of the largest entry (the rows kernel: {err_rows:.2e})"
+
+
+# ------------------------------------------------------------------------------------------------ the stream's kernels alone
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,hidden", [(5, 50), (3, 4100), (300, 64), (9, 1024)])
+@pytest.mark.parametrize("second,depth", [(True, 3), (False, 0), (True, 0), (False, 9)])
+def test_gated_add_with_and_without_the_norm_in_the_kernel(dtype, n, hidden, second, depth):
+    """The gated add (one or two sublayers, with and without a history) alone and followed by the layer norm in the same kernel, against
+    the formulas in float64; widths that are and are not whole 16-byte words; the rows option of the norm."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(n * hidden + depth)
+    rnd = lambda *shape: torch.randn(*shape, generator=g)
+    stream0, a, f = rnd(n, hidden), rnd(n, hidden).to(dtype), rnd(n, hidden).to(dtype) if second else None
+    gates = rnd(n, 2 * hidden + 8).to(dtype)
+    gate_bias, a_bias, w, b = rnd(2 * hidden), rnd(hidden), 1 + 0.1 * rnd(hidden), rnd(hidden)
+    history0 = rnd(depth + 1, n, hidden) if depth else None
+    mixw = rnd(depth + 1) if depth else None
+    eps = 1e-5
+    # the formulas
+    x = stream0.double() + (a.double() + a_bias.double()) * torch.sigmoid(gates[:, :hidden].double() + gate_bias[:hidden].double())
+    if second:
+        x = x + f.double() * torch.sigmoid(gates[:, hidden:2 * hidden].double() + gate_bias[hidden:].double())
+    new_stream = x
+    if depth:
+        new_stream = sum(mixw[j].double() * history0[j].double() for j in range(depth)) + mixw[depth].double() * x
+    mean = new_stream.mean(-1, keepdim=True)
+    want_h = (new_stream - mean) / torch.sqrt(((new_stream - mean) ** 2).mean(-1, keepdim=True) + eps) * w.double() + b.double()
+    dev = lambda t: None if t is None else t.to(DEV)
+    for fused in (False, True):
+        stream, history = stream0.clone().to(DEV), dev(None if history0 is None else history0.clone())
+        kw = dict(gates=dev(gates), gate_bias=dev(gate_bias), a_bias=dev(a_bias), history=history, index=depth, weights=dev(mixw))
+        if fused:
+            h = ops.gated_residual(stream, dev(a), dev(f), norm=(dev(w), dev(b), eps), out_dtype=dtype, **kw)
+        else:
+            assert ops.gated_residual(stream, dev(a), dev(f), **kw) is stream
+            h = ops.stream_layer_norm(stream, dev(w), dev(b), eps, dtype)
+            some = torch.tensor([n - 1, 0], dtype=torch.int32, device=DEV)
+            assert torch.equal(ops.stream_layer_norm(stream, dev(w), dev(b), eps, dtype, rows=some), h[some.long()])
+        assert (stream.cpu().double() - new_stream).abs().max() < 1e-4 * (1 + new_stream.abs().max()), f"stream, fused={fused}"
+        if depth:
+            assert (history[depth].cpu().double() - x).abs().max() < 1e-4 * (1 + x.abs().max()), f"history entry, fused={fused}"
+            assert torch.equal(history[:depth].cpu(), history0[:depth]), "earlier history entries were touched"
+        tol = 2e-5 if dtype == torch.float32 else 2e-2
+        assert (h.cpu().double() - want_h).abs().max() < tol * (1 + want_h.abs().max()), f"norm output, fused={fused}"
