@@ -40,7 +40,8 @@ class RequestCache:
     """Tokens that the pages held so far can take (the shortest table times the page size): lets the two calls that every
     request makes in every step, ``reserve`` and ``advance``, answer the common case with one comparison."""
     released: list[int] = field(default_factory=list)
-    """Per group: how many pages at the front of the table a window has passed and given back."""
+    """Per group: index of the first page of the table that a window has not passed yet; the pages before it have been given back, except
+    the group's ``kept_pages`` at the very front (those hold the first keys, which stay visible)."""
     serial: int = field(default_factory=itertools.count().__next__)
     """Unlike ``id()``, never given to a second request of this process: (serial, version) names one state of one
     request's tables for good."""
@@ -60,6 +61,8 @@ class CacheManager:
         self.pools = [PagePool(num_pages) for _ in plan.groups]
         self.windows = [g.need.window for g in plan.groups]
         self.chunks = [g.need.chunk for g in plan.groups]
+        self.kept_pages = [pages_for(g.need.keep_first, page_size) if g.need.window > 0 else 0 for g in plan.groups]
+        """Per group: pages at the front of every table that a window never passes (they hold the first keys, which stay visible)."""
         self._windowed = [g for g in range(len(plan.groups)) if self.windows[g] > 0 or self.chunks[g] > 0]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._open: dict[int, RequestCache] = {}
@@ -169,8 +172,8 @@ class CacheManager:
         for g in self._windowed:
             table, pool = rc.tables[g], self.pools[g]
             keep_from = min(self._first_needed_page(g, new_length), len(table))  # the next query sits at position new_length
-            done = rc.released[g]
-            if keep_from > done:   # the pages given back are a prefix of the table: only what is new is touched
+            done = max(rc.released[g], self.kept_pages[g])
+            if keep_from > done:   # the pages given back are one stretch of the table: only what is new is touched
                 pool.release(table[done:keep_from])
                 table[done:keep_from] = [RELEASED] * (keep_from - done)
                 rc.released[g] = keep_from
@@ -217,9 +220,9 @@ class CacheManager:
             if rc.room != self._room(rc) and rc.tables:
                 raise AssertionError(f"request {rc.key!r}: room {rc.room} does not match its tables")
             for g, table in enumerate(rc.tables):
-                k = rc.released[g]
-                if any(p != RELEASED for p in table[:k]) or any(p == RELEASED for p in table[k:]):
-                    raise AssertionError(f"request {rc.key!r}, group {g}: the released pages are not the first {k}")
+                k, kept = rc.released[g], min(self.kept_pages[g], rc.released[g])
+                if any(p == RELEASED for p in table[:kept]) or any(p != RELEASED for p in table[kept:k]) or any(p == RELEASED for p in table[k:]):
+                    raise AssertionError(f"request {rc.key!r}, group {g}: the released pages are not those from {kept} to {k}")
         slots = [rc.state_slot for rc in self._open.values()]
         if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
             raise AssertionError("a state slot is held twice or is both held and free")

@@ -51,6 +51,7 @@ struct AttnArgs {
     const float* dist_bias = nullptr;    // [bias_rows, H] fp32 added to the scaled score by distance p - j (last row: all larger ones)
     int bias_rows = 0;
     const float* sink = nullptr;         // [H] fp32: exp(sink) joins the softmax denominator (no key, no value, not scaled)
+    int keep_first = 0;                  // with a window: keys j < keep_first stay visible to every later query
 };
 
 // First key that a query at position `pos` sees: the start of its window and of its chunk, whichever is later.
@@ -59,6 +60,38 @@ __device__ __forceinline__ int key_lo(const AttnArgs& a, int pos) {
     if (a.chunk > 0) lo = max(lo, pos / a.chunk * a.chunk);
     return lo;
 }
+
+// The key blocks a tile walks over when its mask has a window that keeps the sequence's first keys in sight: first the blocks
+// that hold kept keys which the tile's window does not reach (`n_kept` blocks from key 0, of which only keys below `kept_end`
+// are fetched and seen), then the blocks from the window's start (`k_first`) on. Where the window reaches into the kept keys there
+// is one stretch from key 0 and the kept keys are told apart element by element.
+struct KeyWalk {
+    int k_lo;        // first key of the window stretch that is fetched
+    int k_first;     // k_lo rounded down to a block
+    int n_kept;      // blocks of the kept stretch
+    int kept_end;    // keys below it are fetched in the kept stretch
+    int keep;        // what the window stretch's elements compare with: keys below it are seen whatever the window
+    __device__ __forceinline__ int key0(int b, int bn) const { return b < n_kept ? b * bn : k_first + (b - n_kept) * bn; }
+    __device__ __forceinline__ int lo(int b) const { return b < n_kept ? 0 : k_lo; }
+    __device__ __forceinline__ int end(int b, int k_end) const { return b < n_kept ? kept_end : k_end; }
+};
+__device__ __forceinline__ KeyWalk key_walk(const AttnArgs& a, int first_pos, int bn) {
+    KeyWalk w;
+    w.k_lo = key_lo(a, first_pos);
+    w.n_kept = 0; w.kept_end = 0; w.keep = 0;
+    if (a.window > 0 && a.keep_first > 0) {
+        if (a.keep_first >= w.k_lo) {
+            w.k_lo = 0;                      // one stretch from the sequence's start
+            w.keep = a.keep_first;
+        } else {
+            w.kept_end = a.keep_first;
+            w.n_kept = (a.keep_first + bn - 1) / bn;
+        }
+    }
+    w.k_first = (w.k_lo / bn) * bn;
+    return w;
+}
+
 
 template <typename T> struct Vec;   // 16-byte vectors of T
 template <> struct Vec<float> {
@@ -345,13 +378,14 @@ __device__ __forceinline__ const bf16* kv_elem(const bf16* base, int row, int d)
 
 // One warp: S = Q K^T for its 16 rows and NK keys starting at Kw, masked online softmax, O += P V.
 // qf: Q fragments when Q_IN_REGS, else read from Qw (this warp's 16 rows in shared memory).
-// row_lo: the first key each row sees (window, chunk); row_bias: null, or the row's column of a bias-by-distance table
+// row_lo: the first key each row sees (window, chunk), keys below `keep` are seen as well; row_bias: null, or the row's column of a bias-by-distance table
 // [bias_rows, bias_stride] that is added (in natural-log units) to the scaled score.
 template <int NK, bool SWZ = false, bool QREG = Q_IN_REGS>
 __device__ __forceinline__ void warp_block_ex(const uint32_t (&qf)[QREG ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
                                               const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
                                               const int (&row_lo)[2], const float* const (&row_bias)[2], int bias_rows, int bias_stride,
-                                              bool full_block, float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DT8][4]) {
+                                              bool full_block, float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DT8][4],
+                                              int keep = 0) {
     constexpr int NT = NK / 8;
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NT][4];
@@ -391,7 +425,7 @@ __device__ __forceinline__ void warp_block_ex(const uint32_t (&qf)[QREG ? KSTEPS
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 const int kp = key0 + i * 8 + 2 * t + (e & 1);
-                const bool seen = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
+                const bool seen = row_ok[r] && kp <= row_pos[r] && (kp >= row_lo[r] || kp < keep);
                 float v = s[i][e] * scale_log2;
                 if (seen && row_bias[r] != nullptr) v = fmaf(row_bias[r][(size_t)min(row_pos[r] - kp, bias_rows - 1) * bias_stride], LOG2E, v);
                 s[i][e] = seen ? v : -INFINITY;
@@ -529,12 +563,11 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     const int* table_row = a.block_table + (size_t)g.req * a.table_width;
 
     const int k_end = g.pos0 + g.tok_end;
-    const int k_lo = key_lo(a, g.pos0 + g.tok0);
-    const int k_first = (k_lo / MMA_BN) * MMA_BN;
-    const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+    const KeyWalk kw = key_walk(a, g.pos0 + g.tok0, MMA_BN);
+    const int n_blocks = kw.n_kept + (k_end - kw.k_first + MMA_BN - 1) / MMA_BN;
 
     load_q_rows(Qs, q, a, g, PREFILL_ROWS);
-    load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, k_first, k_lo, k_end, g.req);
+    load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, kw.key0(0, MMA_BN), kw.lo(0), kw.end(0, k_end), g.req);
     cp_async_commit();
 
     int row_pos[2], row_head[2], row_lo[2];
@@ -575,7 +608,7 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         const int stage = b & 1;
         if (b + 1 < n_blocks)
             load_kv_block(Ks + (stage ^ 1) * MMA_BN * LDS, Vs + (stage ^ 1) * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
-                          k_first + (b + 1) * MMA_BN, k_lo, k_end, g.req);
+                          kw.key0(b + 1, MMA_BN), kw.lo(b + 1), kw.end(b + 1, k_end), g.req);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -586,14 +619,19 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
                     ldsm_x4(qf[kk], Qw + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
             }
         }
-        const int key0 = k_first + b * MMA_BN;
-        if (key0 <= warp_last_pos) {
+        const int key0 = kw.key0(b, MMA_BN);
+        if (b < kw.n_kept) {
+            // a block of kept first keys behind every row's window: the keys below kept_end are seen by all rows
+            const int none[2] = {0x7fffffff, 0x7fffffff};
+            warp_block_ex<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, none, row_bias,
+                                  a.bias_rows, a.H, false, scale_log2, m, l, o, kw.kept_end);
+        } else if (key0 <= warp_last_pos) {
             // every row of the warp holds a (token, head), the block ends at or before the earliest row's position and
             // starts inside the latest row's window
             const bool full_block = warp_all_rows && key0 + MMA_BN - 1 <= warp_first_pos && key0 >= key_lo(a, warp_last_pos) &&
                                     a.dist_bias == nullptr;
             warp_block_ex<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, row_lo, row_bias,
-                                  a.bias_rows, a.H, full_block, scale_log2, m, l, o);
+                                  a.bias_rows, a.H, full_block, scale_log2, m, l, o, kw.keep);
         }
         __syncthreads();   // everyone is done with this stage before the next prefetch overwrites it
     }
@@ -743,12 +781,12 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     float* my_o = part_o + (unit * splits + split) * DECODE_ROWS * D;
     const int rows_live = g.tok0 < g.tok_end ? (g.tok_end - g.tok0) * g.heads_per_tile : 0;   // rows 0..rows_live-1 may hold a (token, head)
 
-    int first = 0, count = 0, k_lo = 0, k_end = 0, k_first = 0;
+    int first = 0, count = 0, k_end = 0;
+    KeyWalk kw = {};
     if (rows_live > 0) {
         k_end = g.pos0 + g.tok_end;
-        k_lo = key_lo(a, g.pos0 + g.tok0);
-        k_first = (k_lo / MMA_BN) * MMA_BN;
-        const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
+        kw = key_walk(a, g.pos0 + g.tok0, MMA_BN);
+        const int n_blocks = kw.n_kept + (k_end - kw.k_first + MMA_BN - 1) / MMA_BN;
         const int per = (n_blocks + splits - 1) / splits;
         first = split * per;
         count = max(0, min(per, n_blocks - first));
@@ -762,7 +800,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
         for (int st = 0; st < DECODE_STAGES - 1; ++st) {
             if (st < count)
                 load_kv_block(Ks + st * MMA_BN * LDS, Vs + st * MMA_BN * LDS, k_cache, v_cache, table_row, a, g.kvh,
-                              k_first + (first + st) * MMA_BN, k_lo, k_end, g.req);
+                              kw.key0(first + st, MMA_BN), kw.lo(first + st), kw.end(first + st, k_end), g.req);
             cp_async_commit();
         }
         int row_pos[2], row_lo[2];
@@ -791,7 +829,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             const int nb = b + DECODE_STAGES - 1;
             if (nb < count)
                 load_kv_block(Ks + (nb % DECODE_STAGES) * MMA_BN * LDS, Vs + (nb % DECODE_STAGES) * MMA_BN * LDS, k_cache, v_cache,
-                              table_row, a, g.kvh, k_first + (first + nb) * MMA_BN, k_lo, k_end, g.req);
+                              table_row, a, g.kvh, kw.key0(first + nb, MMA_BN), kw.lo(first + nb), kw.end(first + nb, k_end), g.req);
             cp_async_commit();
             cp_async_wait<DECODE_STAGES - 1>();
             __syncthreads();
@@ -802,12 +840,19 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                         ldsm_x4(qf[kk], Qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LDS + kk * 16 + 8 * (lane >> 4));
                 }
             }
-            const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
-            // rows without a (token, head) have zero queries: unmasked they give finite numbers that are never stored,
-            // so the block counts as fully visible when the rows that do exist see all of it
-            const bool full_block = key0 + 15 <= tile_first_pos && key0 >= key_lo(a, tile_last_pos) && a.dist_bias == nullptr;
-            warp_block_ex<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
-                              row_ok, row_lo, row_bias, a.bias_rows, a.H, full_block, scale_log2, m, l, o);
+            const int key0 = kw.key0(first + b, MMA_BN) + warp * 16;   // this warp's quarter of the block
+            if (first + b < kw.n_kept) {
+                // kept first keys behind every row's window: those below kept_end are seen by all rows
+                const int none[2] = {0x7fffffff, 0x7fffffff};
+                warp_block_ex<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
+                                  row_ok, none, row_bias, a.bias_rows, a.H, false, scale_log2, m, l, o, kw.kept_end);
+            } else {
+                // rows without a (token, head) have zero queries: unmasked they give finite numbers that are never stored,
+                // so the block counts as fully visible when the rows that do exist see all of it
+                const bool full_block = key0 + 15 <= tile_first_pos && key0 >= key_lo(a, tile_last_pos) && a.dist_bias == nullptr;
+                warp_block_ex<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
+                                  row_ok, row_lo, row_bias, a.bias_rows, a.H, full_block, scale_log2, m, l, o, kw.keep);
+            }
             __syncthreads();
         }
 #pragma unroll
@@ -2224,6 +2269,7 @@ struct MaskExtras {
     const float* dist_bias = nullptr;
     int bias_rows = 0;
     const float* sink = nullptr;
+    int keep_first = 0;
 };
 
 static int paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
@@ -2245,17 +2291,19 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
                                 long_rows, q_tokens, cut, status, stream, MaskExtras{});
 }
 
-// The same attention with the extras of AttnArgs: a chunk mask, a bias by distance and a sink (see there). These run on the
+// The same attention with the extras of AttnArgs: a chunk mask, first keys kept in sight behind a window, a bias by distance and a sink (see there). These run on the
 // cp.async tensor-core kernels only: no kv_maps, long tiles of 64 rows, cut 0.
 OXR_API int oxr_paged_attention_masked_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                             const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                             const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                             const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
-                                            float scale, int window, int chunk, const float* dist_bias, int bias_rows, const float* sink,
-                                            int splits, float* part_o, float* part_ml, int* counters, int* status, cudaStream_t stream) {
-    if (chunk < 0 || (dist_bias != nullptr && bias_rows <= 0)) return OXR_BAD_ARGUMENT;
+                                            float scale, int window, int chunk, int keep_first, const float* dist_bias, int bias_rows,
+                                            const float* sink, int splits, float* part_o, float* part_ml, int* counters, int* status,
+                                            cudaStream_t stream) {
+    if (chunk < 0 || keep_first < 0 || (dist_bias != nullptr && bias_rows <= 0)) return OXR_BAD_ARGUMENT;
     MaskExtras extras;
     extras.chunk = chunk; extras.dist_bias = dist_bias; extras.bias_rows = bias_rows; extras.sink = sink;
+    extras.keep_first = window > 0 ? keep_first : 0;
     return paged_attention_bf16(out, q, k_cache, v_cache, short_req, short_tok0, n_short, long_req, long_tok0, n_long, cu_q, ctx_lens, block_table,
                                 table_width, page_size, num_pages, H, KV, scale, window, splits, part_o, part_ml, counters, nullptr, 0,
                                 PREFILL_ROWS, 0, 0, status, stream, extras);
@@ -2269,7 +2317,7 @@ static int paged_attention_bf16(void* out, const void* q, const void* k_cache, c
                                 const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int cut, int* status, cudaStream_t stream,
                                 const MaskExtras& extras) {
     if (n_short <= 0 && n_long <= 0) return 0;
-    const bool masked = extras.chunk > 0 || extras.dist_bias != nullptr || extras.sink != nullptr;
+    const bool masked = extras.chunk > 0 || extras.dist_bias != nullptr || extras.sink != nullptr || extras.keep_first > 0;
     if (masked && (kv_maps != nullptr || cut != 0 || (n_long > 0 && long_rows != PREFILL_ROWS))) return OXR_BAD_ARGUMENT;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
     if ((splits > 1 || cut != 0) && n_short > 0 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
@@ -2289,7 +2337,7 @@ static int paged_attention_bf16(void* out, const void* q, const void* k_cache, c
     for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
     a.scale = scale; a.window = window; a.status = status;
-    a.chunk = extras.chunk; a.dist_bias = extras.dist_bias; a.bias_rows = extras.bias_rows; a.sink = extras.sink;
+    a.chunk = extras.chunk; a.dist_bias = extras.dist_bias; a.bias_rows = extras.bias_rows; a.sink = extras.sink; a.keep_first = extras.keep_first;
     if (n_long > 0 && long_rows == BIG_ROWS) {
         // long tiles of 256 rows: the tcgen05 kernel (the host made the tile list for 256 rows)
         if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3 || !(scale > 0.f)) return OXR_BAD_ARGUMENT;

@@ -3,7 +3,7 @@
 //   * key size DK and value size DV differ freely; values may be the first DV entries of the key rows (a latent cache:
 //     one shared row per token that is both key and value);
 //   * mask: causal, optionally within chunks counted from position 0 (i sees j <= i with floor(i/chunk) == floor(j/chunk))
-//     or within a window (the last `window` keys);
+//     or within a window (the last `window` keys), beside which the first `keep_first` keys of the sequence stay visible;
 //   * an additive bias by distance, read from a table [distances, heads] (the last row stands for every larger distance);
 //   * a sink: a per-head number that joins the softmax denominator as exp(sink) and has no value.
 //
@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
     T* __restrict__ out, const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, long long k_slot_stride, int k_head_stride,
     const T* __restrict__ v_pool, long long v_slot_stride, int v_head_stride, int DK, int DV, int H, int KVH, const int* __restrict__ positions,
     const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_width, int page_size, int num_pages, float scale,
-    int chunk, int window, const float* __restrict__ dist_bias, int bias_rows, const float* __restrict__ sink, int* status) {
+    int chunk, int window, int keep_first, const float* __restrict__ dist_bias, int bias_rows, const float* __restrict__ sink, int* status) {
     extern __shared__ float q_smem[];   // [warps, DK]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int t = blockIdx.x, h = blockIdx.y * warps + warp;
@@ -44,9 +44,12 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
 #pragma unroll
     for (int i = 0; i < DVC; ++i) acc[i] = 0.f;
 
-    for (int j0 = lo; j0 <= p; j0 += 32) {
+    // two stretches of keys: the sequence's first keys that stay visible behind the window (none without one), then the window
+    const int kept_end = min(keep_first, lo);
+    for (int j0 = kept_end > 0 ? 0 : lo; j0 <= p; j0 = (j0 < lo && j0 + 32 >= kept_end) ? lo : j0 + 32) {
+        const int last = j0 < lo ? kept_end - 1 : p;      // last key of this stretch
         const int j = j0 + lane;
-        const bool seen = j <= p;
+        const bool seen = j <= last;
         long long slot = 0;
         float s = -INFINITY;
         if (seen) {
@@ -73,7 +76,7 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
         m = m_new;
 #pragma unroll
         for (int i = 0; i < DVC; ++i) acc[i] *= corr;
-        const int count = min(32, p - j0 + 1);
+        const int count = min(32, last - j0 + 1);
         for (int jj = 0; jj < count; ++jj) {
             const float wj = __shfl_sync(0xffffffffu, w, jj);
             const long long sj = __shfl_sync(0xffffffffu, slot, jj);
@@ -97,10 +100,10 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
 OXR_API int oxr_attention_rows(void* out, const void* q, int q_stride, const void* k_pool, long long k_slot_stride, int k_head_stride,
                                const void* v_pool, long long v_slot_stride, int v_head_stride, int DK, int DV, int H, int KVH, int n_tokens,
                                const int* positions, const int* req_of_token, const int* block_table, int table_width, int page_size, int num_pages,
-                               float scale, int chunk, int window, const float* dist_bias, int bias_rows, const float* sink, int dtype, int* status,
-                               cudaStream_t stream) {
+                               float scale, int chunk, int window, int keep_first, const float* dist_bias, int bias_rows, const float* sink, int dtype,
+                               int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (DK <= 0 || DV <= 0 || DV > 32 * ROWS_MAX_DV_CHUNKS || H <= 0 || KVH <= 0 || H % KVH || page_size <= 0 || chunk < 0 || window < 0 ||
+    if (DK <= 0 || DV <= 0 || DV > 32 * ROWS_MAX_DV_CHUNKS || H <= 0 || KVH <= 0 || H % KVH || page_size <= 0 || chunk < 0 || window < 0 || keep_first < 0 ||
         (dist_bias != nullptr && bias_rows <= 0))
         return OXR_BAD_ARGUMENT;
     const int warps = H >= 4 ? 4 : H;
@@ -111,7 +114,7 @@ OXR_API int oxr_attention_rows(void* out, const void* q, int q_stride, const voi
 #define OXR_ROWS(T, DVC) \
     attn_rows_kernel<T, DVC><<<grid, 32 * warps, smem, stream>>>((T*)out, (const T*)q, q_stride, (const T*)k_pool, k_slot_stride, k_head_stride, \
                                                                 (const T*)v_pool, v_slot_stride, v_head_stride, DK, DV, H, KVH, positions, req_of_token, \
-                                                                block_table, table_width, page_size, num_pages, scale, chunk, window, dist_bias, \
+                                                                block_table, table_width, page_size, num_pages, scale, chunk, window, keep_first, dist_bias, \
                                                                 bias_rows, sink, status)
     if (dtype == 0) {
         if (DV <= 128) OXR_ROWS(float, 4);

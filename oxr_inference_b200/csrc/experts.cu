@@ -354,3 +354,77 @@ OXR_API int oxr_combine_rows(void* out, const void* y, const int* place, const f
     else combine_rows_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)y, place, weights, top, width);
     return oxr_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------- SiLU-gated experts
+// The SiLU-gated unit over the stacked columns of all experts: gu[t] = E stretches [gate (ff) | up (ff)], one per expert. With the
+// token's weight w = gate_w[t, e] for expert e (0: not chosen; gate_w None: 1):
+//   on_input:  a[t, e ff + c] = silu(w g) * (w u)      the weight multiplies what the expert READS (W (w h) = w (W h))
+//   else:      a[t, e ff + c] = w * silu(g) * u
+template <typename T>
+__global__ void expert_silu_glu_kernel(T* __restrict__ a, const T* __restrict__ gu, const float* __restrict__ gate_w, size_t total, int ff, int E,
+                                       int on_input) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int cols = E * ff;
+    const size_t t = i / cols;
+    const int c = (int)(i - t * cols), e = c / ff, k = c - e * ff;
+    const float w = gate_w != nullptr ? gate_w[t * E + e] : 1.f;
+    const T* src = gu + t * 2 * cols + (size_t)e * 2 * ff;
+    float g = Num<T>::to_f32(src[k]), u = Num<T>::to_f32(src[ff + k]), out;
+    if (on_input) {
+        g *= w;
+        u *= w;
+        out = g / (1.f + expf(-g)) * u;
+    } else {
+        out = w * (g / (1.f + expf(-g)) * u);
+    }
+    a[i] = Num<T>::from_f32(w == 0.f ? 0.f : out);
+}
+
+OXR_API int oxr_expert_silu_glu(void* a, const void* gu, const float* gate_w, int n_tokens, int E, int ff, int on_input, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (E <= 0 || ff <= 0) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n_tokens * E * ff;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) expert_silu_glu_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)gu, gate_w, total, ff, E, on_input);
+    else expert_silu_glu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)gu, gate_w, total, ff, E, on_input);
+    return oxr_launch_status();
+}
+
+// x[place[p]] *= weights[p] for every (token, choice) pair p: rows gathered by expert, each scaled by its pair's weight (fp32 product,
+// rounded once). One block per pair.
+template <typename T>
+__global__ void scale_placed_rows_kernel(T* __restrict__ x, const int* __restrict__ place, const float* __restrict__ weights, int hidden) {
+    const int row = place[blockIdx.x];
+    if (row < 0) return;
+    const float w = weights[blockIdx.x];
+    T* dst = x + (size_t)row * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<T>::from_f32(Num<T>::to_f32(dst[i]) * w);
+}
+
+OXR_API int oxr_scale_placed_rows(void* x, const int* place, const float* weights, int pairs, int hidden, int dtype, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    if (dtype == 0) scale_placed_rows_kernel<float><<<pairs, 128, 0, stream>>>((float*)x, place, weights, hidden);
+    else scale_placed_rows_kernel<__nv_bfloat16><<<pairs, 128, 0, stream>>>((__nv_bfloat16*)x, place, weights, hidden);
+    return oxr_launch_status();
+}
+
+// y[t] += sigmoid(z[t]) * s[t]: a second feed-forward's result joins the first's, multiplied by one gate per token (z fp32 logits).
+template <typename T>
+__global__ void add_row_gated_kernel(T* __restrict__ y, const T* __restrict__ s, const float* __restrict__ z, int hidden, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float g = 1.f / (1.f + expf(-z[i / hidden]));
+    y[i] = Num<T>::from_f32(Num<T>::to_f32(y[i]) + g * Num<T>::to_f32(s[i]));
+}
+
+OXR_API int oxr_add_row_gated(void* y, const void* s, const float* z, int n, int hidden, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n * hidden;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0) add_row_gated_kernel<float><<<blocks, 256, 0, stream>>>((float*)y, (const float*)s, z, hidden, total);
+    else add_row_gated_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)s, z, hidden, total);
+    return oxr_launch_status();
+}

@@ -200,11 +200,11 @@ OXR_API int oxr_mlstm_scan(float* y, float* coef, const void* proj, int n_reques
     return oxr_launch_status();
 }
 
-// out[t, h, d] = y[t, h, d] / rms(y[t, h, :]) * weight[h, d] * sigmoid(gate[t, gate_col0 + h DV + d]); one warp per (token, head),
-// everything in fp32, rounded once to T.
+// out[t, h, d] = y[t, h, d] / rms(y[t, h, :]) * weight[h, d] * act(gate[t, gate_col0 + h DV + d]) with act = sigmoid, or silu when `silu`;
+// one warp per (token, head), everything in fp32, rounded once to T.
 template <typename T>
 __global__ void head_norm_gate_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate, int gate_stride, int gate_col0,
-                                      const float* __restrict__ weight, int heads, int DV, float eps) {
+                                      const float* __restrict__ weight, int heads, int DV, float eps, int silu) {
     const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     const int t = blockIdx.x, h = blockIdx.y * warps + (threadIdx.x >> 5);
     if (h >= heads) return;
@@ -214,18 +214,18 @@ __global__ void head_norm_gate_kernel(T* __restrict__ out, const float* __restri
     const float inv = 1.f / sqrtf(warp_sum(sq) / (float)DV + eps);
     for (int d = lane; d < DV; d += 32) {
         const float g = Num<T>::to_f32(gate[(size_t)t * gate_stride + gate_col0 + h * DV + d]);
-        out[((size_t)t * heads + h) * DV + d] = Num<T>::from_f32(o[d] * inv * weight[h * DV + d] * (1.f / (1.f + expf(-g))));
+        out[((size_t)t * heads + h) * DV + d] = Num<T>::from_f32(o[d] * inv * weight[h * DV + d] * ((silu ? g : 1.f) / (1.f + expf(-g))));
     }
 }
 
 OXR_API int oxr_head_norm_gate(void* out, const float* y, const void* gate, int n_tokens, int gate_stride, int gate_col0, const float* weight,
-                               int heads, int DV, float eps, int dtype, cudaStream_t stream) {
+                               int heads, int DV, float eps, int silu, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (heads <= 0 || DV <= 0) return OXR_BAD_ARGUMENT;
     const int warps = heads >= 4 ? 4 : heads;
     dim3 grid(n_tokens, (heads + warps - 1) / warps);
     if (grid.y > 65535) return OXR_BAD_ARGUMENT;
-    if (dtype == 0) head_norm_gate_kernel<float><<<grid, 32 * warps, 0, stream>>>((float*)out, y, (const float*)gate, gate_stride, gate_col0, weight, heads, DV, eps);
-    else head_norm_gate_kernel<__nv_bfloat16><<<grid, 32 * warps, 0, stream>>>((__nv_bfloat16*)out, y, (const __nv_bfloat16*)gate, gate_stride, gate_col0, weight, heads, DV, eps);
+    if (dtype == 0) head_norm_gate_kernel<float><<<grid, 32 * warps, 0, stream>>>((float*)out, y, (const float*)gate, gate_stride, gate_col0, weight, heads, DV, eps, silu);
+    else head_norm_gate_kernel<__nv_bfloat16><<<grid, 32 * warps, 0, stream>>>((__nv_bfloat16*)out, y, (const __nv_bfloat16*)gate, gate_stride, gate_col0, weight, heads, DV, eps, silu);
     return oxr_launch_status();
 }

@@ -47,6 +47,10 @@ __global__ void norm_add_norm_kernel(float* __restrict__ stream, const T* __rest
         s2 = fmaf(v, v, s2);
     }
     if (out == nullptr) return;
+    if (w_next == nullptr) {   // no norm behind the add: the new stream, rounded
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[at + i] = Num<T>::from_f32(cached ? rowbuf[i] : stream[at + i]);
+        return;
+    }
     s2 = block_sum(s2, red);
     const float inv2 = 1.f / sqrtf(s2 / (float)hidden + eps_next);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -112,6 +116,14 @@ __global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ stream, const __
         }
     }
     if (out == nullptr) return;
+    if (w_next == nullptr) {   // no norm behind the add: the new stream, rounded
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int idx = threadIdx.x + v * blockDim.x;
+            if (idx < nvec) *reinterpret_cast<uint4*>(out + at + 8 * idx) = f32_to_bf16x8(sv[v]);
+        }
+        return;
+    }
     s2 = block_sum(s2, red);
     const float inv2 = 1.f / sqrtf(s2 / (float)hidden + eps_next);
 #pragma unroll
@@ -212,7 +224,7 @@ OXR_API int oxr_stream_rms_norm(void* out, const float* stream, const float* wei
 OXR_API int oxr_norm_add_norm(float* stream, const void* y, const float* w_post, void* out, const float* w_next, int n, int hidden,
                               float eps_post, float eps_next, int dtype, cudaStream_t stream_) {
     if (n <= 0) return 0;
-    if (hidden <= 0 || (out != nullptr && w_next == nullptr)) return OXR_BAD_ARGUMENT;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
     if (dtype == 1 && hidden % 8 == 0 && hidden <= 32768 && (uintptr_t)stream % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
         (uintptr_t)w_post % 16 == 0 && (uintptr_t)w_next % 16 == 0) {
         const int nvec = hidden / 8;
@@ -554,5 +566,48 @@ OXR_API int oxr_add_inplace(void* y, const void* x, long long total, int dtype, 
     if (total <= 0) return 0;
     if (dtype == 0) add_inplace_kernel<float><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((float*)y, (const float*)x, (size_t)total);
     else add_inplace_kernel<__nv_bfloat16><<<grid_for((size_t)total, 256), 256, 0, stream_>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, (size_t)total);
+    return oxr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------- two mixers side by side
+// out[r] = 0.5 * (a[r] / rms(a[r]) * wa + b[r] / rms(b[r]) * wb): the mean of two results, each RMS-normed over the row with a weight of
+// its own; sums of squares, norms and the mean in fp32, rounded once. One block per row.
+template <typename T>
+__global__ void pair_norm_mean_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
+                                      const float* __restrict__ wb, int hidden, float eps) {
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * hidden;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float x = Num<T>::to_f32(a[at + i]), y = Num<T>::to_f32(b[at + i]);
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    sa = block_sum(sa, red);
+    sb = block_sum(sb, red);
+    const float ia = 1.f / sqrtf(sa / (float)hidden + eps), ib = 1.f / sqrtf(sb / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        out[at + i] = Num<T>::from_f32(0.5f * (Num<T>::to_f32(a[at + i]) * ia * wa[i] + Num<T>::to_f32(b[at + i]) * ib * wb[i]));
+}
+
+OXR_API int oxr_pair_norm_mean(void* out, const void* a, const void* b, const float* wa, const float* wb, int n, int hidden, float eps, int dtype,
+                               cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    const int threads = hidden >= 2048 ? 256 : 128;
+    if (dtype == 0) pair_norm_mean_kernel<float><<<n, threads, 0, stream_>>>((float*)out, (const float*)a, (const float*)b, wa, wb, hidden, eps);
+    else pair_norm_mean_kernel<__nv_bfloat16><<<n, threads, 0, stream_>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, hidden, eps);
+    return oxr_launch_status();
+}
+
+// x <- cap * tanh(x / cap), fp32, in place (capped logits).
+__global__ void tanh_cap_kernel(float* __restrict__ x, float cap, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] = cap * tanhf(x[i] / cap);
+}
+
+OXR_API int oxr_tanh_cap(float* x, float cap, long long total, cudaStream_t stream_) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return OXR_BAD_ARGUMENT;
+    tanh_cap_kernel<<<grid_for((size_t)total, 256), 256, 0, stream_>>>(x, cap, (size_t)total);
     return oxr_launch_status();
 }

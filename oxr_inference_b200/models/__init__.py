@@ -1,3 +1,3 @@
 """Architectures this package knows; importing the package registers them."""
 
-from oxr_inference_b200.models import bifusun, qwen3, radapel, vazepel  # noqa: F401
+from oxr_inference_b200.models import bifusun, nidudra, qwen3, radapel, vazepel  # noqa: F401

@@ -134,7 +134,7 @@ def _lib():
         lib.oxr_mamba_conv.argtypes = [p, p, i, i, i, i, i, i, p, p, p, ll, p, p, p, i, p]
         lib.oxr_mamba_scan.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, i, p]
         lib.oxr_gated_group_norm.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
-        lib.oxr_attention_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, i, i, p, i, p, i, p, p]
+        lib.oxr_attention_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, i, i, i, p, i, p, i, p, p]
         lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
@@ -142,7 +142,7 @@ def _lib():
         lib.oxr_add_bias.argtypes = [p, p, i, i, i, p]
         lib.oxr_scale_f32.argtypes = [p, f, ll, p]
         lib.oxr_mlstm_scan.argtypes = [p, p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
-        lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
+        lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, i, p]
         lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, i, i, i, p]
         lib.oxr_gated_relu2.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_expert_sort.argtypes = [p, p, p, p, p, i, i, i, i, p]
@@ -162,6 +162,17 @@ def _lib():
         lib.oxr_attention_mix_mma_smem.argtypes = [i, i, i, i, i, i]
         lib.oxr_attention_mix_mma_smem.restype = c_longlong
         lib.oxr_expert_clamped_glu.argtypes = [p, p, p, i, i, i, f, f, i, p]
+        lib.oxr_head_prep.argtypes = [p, p, p, p, i, i, i, i, i, i, i, i, i, i, i, i, p, p, i, p, ll, i, i, p, p, f, p, p, i, p, ll, p, p, p, i, p, p]
+        lib.oxr_sigmoid_gate.argtypes = [p, p, i, i, i, i, i, i, i, p]
+        lib.oxr_gla_scan.argtypes = [p, p, i, i, i, i, i, p, p, f, i, i, i, f, p, ll, p, p, i, p]
+        lib.oxr_pair_norm_mean.argtypes = [p, p, p, p, p, i, i, f, i, p]
+        lib.oxr_tanh_cap.argtypes = [p, f, ll, p]
+        lib.oxr_expert_silu_glu.argtypes = [p, p, p, i, i, i, i, i, p]
+        lib.oxr_scale_placed_rows.argtypes = [p, p, p, i, i, i, p]
+        lib.oxr_add_row_gated.argtypes = [p, p, p, i, i, i, p]
+        for name in ("oxr_head_prep", "oxr_sigmoid_gate", "oxr_gla_scan", "oxr_pair_norm_mean", "oxr_tanh_cap", "oxr_expert_silu_glu",
+                     "oxr_scale_placed_rows", "oxr_add_row_gated"):
+            getattr(lib, name).restype = c_int
         for name in ("oxr_stream_layer_norm", "oxr_gated_residual", "oxr_gelu_tanh", "oxr_attention_mix_rows", "oxr_bias_rope_store", "oxr_gated_residual_norm",
                      "oxr_expert_clamped_glu"):
             getattr(lib, name).restype = c_int
@@ -194,7 +205,7 @@ def _attn_lib(head_dim: int):
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
         lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, i, i, p, p]
-        lib.oxr_paged_attention_masked_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, i, p, i, p, p, p, p, p]
+        lib.oxr_paged_attention_masked_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, i, p, i, p, i, p, p, p, p, p]
         lib.oxr_paged_attention_masked_bf16.restype = c_int
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
@@ -536,7 +547,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     ctx_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, scale: float, window: int,
                     kv_len_bound: int, status: torch.Tensor, generic: bool = False, kv_maps: KVMaps | None = None,
                     layer_in_pool: int = 0, uneven: bool = False, chunk: int = 0, dist_bias: torch.Tensor | None = None,
-                    sink: torch.Tensor | None = None) -> torch.Tensor:
+                    sink: torch.Tensor | None = None, keep_first: int = 0) -> torch.Tensor:
     """Causal grouped-query attention of the step's new tokens over the paged cache
     (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
     ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys; ``tiles`` maps each
@@ -548,12 +559,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
     bfloat16 only, on the cp.async tensor-core kernels (no ``kv_maps``): ``chunk`` > 0 lets position p see only keys j with
     ``j // chunk == p // chunk``; ``dist_bias [rows, H]`` (fp32) is added to the scaled score by distance p - j (the last row for all
-    larger ones); ``sink [H]`` (fp32) adds ``exp(sink)`` to the softmax denominator. ``v_cache`` may be ``k_cache`` itself (a latent
+    larger ones); ``sink [H]`` (fp32) adds ``exp(sink)`` to the softmax denominator; with a window, ``keep_first`` > 0 keeps the request's
+    first ``keep_first`` keys visible to every later query. ``v_cache`` may be ``k_cache`` itself (a latent
     cache whose rows are key and value at once)."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
-    masked = chunk > 0 or dist_bias is not None or sink is not None
+    keep_first = int(keep_first) if window > 0 else 0
+    masked = chunk > 0 or dist_bias is not None or sink is not None or keep_first > 0
     if masked and (q.dtype != torch.bfloat16 or generic or kv_maps is not None):
         raise KernelError("paged_attention: chunk, dist_bias and sink run on the bfloat16 cp.async kernels only (no kv_maps)")
     for t, nm in ((cu_q, "cu_q"), (ctx_lens, "ctx_lens"), (block_table, "block_table")):
@@ -590,7 +603,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if sink is not None and sink.numel() != num_heads:
             raise KernelError("paged_attention: one sink per head")
         code = lib.oxr_paged_attention_masked_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
-                                                   s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, int(chunk),
+                                                   s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, int(chunk), keep_first,
                                                    _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0, _ptr(sink), splits,
                                                    _ptr(part_o), _ptr(part_ml), _ptr(counters), status.data_ptr(), _stream())
         global launch_count
@@ -1059,9 +1072,10 @@ def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_
 
 
 def norm_add_norm(stream: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float, next_weight: torch.Tensor | None = None,
-                  next_eps: float = 0.0) -> torch.Tensor | None:
+                  next_eps: float = 0.0, rounded: bool = False) -> torch.Tensor | None:
     """In place ``stream += rmsnorm(y) * post_weight`` (fp32); with ``next_weight`` also returns ``rmsnorm(stream) * next_weight`` in
-    ``y.dtype``: a sublayer's post-norm, the residual add and the next sublayer's pre-norm in one pass over the row."""
+    ``y.dtype``: a sublayer's post-norm, the residual add and the next sublayer's pre-norm in one pass over the row. ``rounded`` (without a
+    next weight): also returns the new stream rounded to ``y.dtype``, for a sublayer that reads the stream itself."""
     _need(stream, "stream", torch.float32)
     _need(y, "y")
     _need(post_weight, "post_weight", torch.float32)
@@ -1071,6 +1085,7 @@ def norm_add_norm(stream: torch.Tensor, y: torch.Tensor, post_weight: torch.Tens
     out = None
     if next_weight is not None:
         _need(next_weight, "next_weight", torch.float32)
+    if next_weight is not None or rounded:
         out = torch.empty((n, hidden), dtype=y.dtype, device=y.device)
     _done(_lib().oxr_norm_add_norm(stream.data_ptr(), y.data_ptr(), post_weight.data_ptr(), _ptr(out), _ptr(next_weight), n, hidden, float(post_eps),
                                    float(next_eps), _dtype_code(y), _stream()), "norm_add_norm")
@@ -1451,14 +1466,15 @@ def head_linear(out: torch.Tensor, out0: int, x: torch.Tensor, x0: int, weight: 
 
 
 def attention_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor | None, *, value_dim: int, positions: torch.Tensor,
-                   req_of_token: torch.Tensor, block_table: torch.Tensor, scale: float, chunk: int = 0, window: int = 0,
+                   req_of_token: torch.Tensor, block_table: torch.Tensor, scale: float, chunk: int = 0, window: int = 0, keep_first: int = 0,
                    dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None, status: torch.Tensor) -> torch.Tensor:
     """Attention of the step's tokens over the paged cache with the mask and every size as an argument, in fp32 arithmetic.
 
     ``q [tokens, >= H * DK]``: the queries are the first ``H * DK`` columns (so a stacked q|k|v product can be handed over as it is);
     ``k_pool [pages, page_size, KV, DK]``; ``v_pool [pages, page_size, KV, DV]`` or None, when the values are the first ``value_dim`` entries
     of the key rows (a latent cache). Token t at position p of its request sees keys j <= p, within its chunk of ``chunk`` positions
-    (counted from 0) and within its last ``window`` keys when those are given. ``dist_bias [rows, H]`` (fp32) is added to the scaled score by
+    (counted from 0) and within its last ``window`` keys when those are given; with a window the request's first ``keep_first`` keys stay
+    visible too. ``dist_bias [rows, H]`` (fp32) is added to the scaled score by
     distance p - j (the last row for all larger ones); ``sink [H]`` adds ``exp(sink)`` to the softmax denominator.
     Returns ``[tokens, H * value_dim]``."""
     _need(q, "q")
@@ -1487,7 +1503,7 @@ def attention_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool
     out = torch.empty((n, H * value_dim), dtype=q.dtype, device=q.device)
     _done(_lib().oxr_attention_rows(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), KV * DK, DK, v.data_ptr(), v_slot, v_head, DK, value_dim, H,
                                     KV, n, positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, pages,
-                                    float(scale), int(chunk), int(window), _ptr(dist_bias), bias_rows, _ptr(sink), _dtype_code(q), status.data_ptr(),
+                                    float(scale), int(chunk), int(window), int(keep_first) if window > 0 else 0, _ptr(dist_bias), bias_rows, _ptr(sink), _dtype_code(q), status.data_ptr(),
                                     _stream()), "attention_rows")
     return out
 
@@ -1598,9 +1614,9 @@ def mlstm_scan(proj: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, gates:
     return y
 
 
-def head_norm_gate(y: torch.Tensor, proj: torch.Tensor, gate_col0: int, weight: torch.Tensor, heads: int, eps: float) -> torch.Tensor:
-    """``y [tokens, heads * d]`` (fp32): every head's stretch divided by its own root mean square, times ``weight``, times the sigmoid of the columns
-    ``[gate_col0, gate_col0 + heads * d)`` of ``proj``; rounded to ``proj.dtype``."""
+def head_norm_gate(y: torch.Tensor, proj: torch.Tensor, gate_col0: int, weight: torch.Tensor, heads: int, eps: float, silu: bool = False) -> torch.Tensor:
+    """``y [tokens, heads * d]`` (fp32): every head's stretch divided by its own root mean square, times ``weight``, times the sigmoid (``silu``:
+    the SiLU) of the columns ``[gate_col0, gate_col0 + heads * d)`` of ``proj``; rounded to ``proj.dtype``."""
     _need(y, "y", torch.float32)
     _need(proj, "proj")
     _need(weight, "weight", torch.float32)
@@ -1609,7 +1625,7 @@ def head_norm_gate(y: torch.Tensor, proj: torch.Tensor, gate_col0: int, weight: 
         raise KernelError("head_norm_gate: sizes do not fit")
     out = torch.empty((n, inner), dtype=proj.dtype, device=y.device)
     _done(_lib().oxr_head_norm_gate(out.data_ptr(), y.data_ptr(), proj.data_ptr(), n, proj.shape[1], gate_col0, weight.data_ptr(), heads, inner // heads,
-                                    float(eps), _dtype_code(proj), _stream()), "head_norm_gate")
+                                    float(eps), int(bool(silu)), _dtype_code(proj), _stream()), "head_norm_gate")
     return out
 
 
@@ -1739,3 +1755,166 @@ def combine_rows(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor) ->
     _done(_lib().oxr_combine_rows(out.data_ptr(), y.data_ptr(), place.data_ptr(), weights.data_ptr(), n, top, y.shape[1], _dtype_code(y), _stream()),
           "combine_rows")
     return out
+
+
+# --------------------------------------------------------------------------------------------------- heads between projection and attention
+HEAD_NORMS = {None: 0, "weighted": 1, "unit": 2}
+
+
+def head_prep(proj: torch.Tensor, *, q_col0: int, k_col0: int | None, v_col0: int | None, values_are_keys: bool = False, num_heads: int,
+              num_kv_heads: int, key_dim: int, value_dim: int, bias: torch.Tensor | None = None, taps: torch.Tensor | None = None,
+              tails: torch.Tensor | None = None, norm: str | None = None, norm_after_rotation: bool = False, q_weight: torch.Tensor | None = None,
+              k_weight: torch.Tensor | None = None, eps: float = 0.0, cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
+              k_pool: torch.Tensor | None = None, v_pool: torch.Tensor | None = None, slots: torch.Tensor, req_of_token: torch.Tensor,
+              cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int, status: torch.Tensor) -> torch.Tensor:
+    """Query and key heads on their way from the projections ``proj [tokens, *]`` to attention, and the cache write. In this order, each step
+    optional: ``bias [H DK + KV DK]`` (fp32, q then k) is added; every channel passes a causal filter ``taps [channels, n]`` (the last tap on
+    the current token; earlier tokens come from the step's rows or from the request's row of ``tails``, fp32 ``[slots, channels * (n - 1)]``,
+    which is moved on afterwards); with ``values_are_keys`` the filtered keys are stored as the values; every head is RMS-normed
+    (``norm="weighted"``: times ``q_weight`` / ``k_weight [DK]``; ``"unit"``: no weight) before or after the rotation; the pairs
+    ``(i, i + half)`` of each head's first ``2 half`` entries turn by the token's angles (``cos``, ``sin`` fp32 ``[tokens, half]``). Keys and
+    values go to ``k_pool`` / ``v_pool [pages, page_size, KV, D]`` at ``slots`` (-1: not stored); ``k_col0`` None: queries only. Returns
+    ``q [tokens, H * DK]``. All arithmetic fp32, one rounding."""
+    _need(proj, "proj")
+    n = proj.shape[0]
+    H, KV, DK, DV = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
+    has_k = k_col0 is not None
+    v_mode = 0 if not has_k else (2 if values_are_keys else (1 if v_col0 is not None else 0))
+    pool_slots = 0
+    if has_k:
+        _need(k_pool, "k_pool", proj.dtype)
+        _need(v_pool, "v_pool", proj.dtype)
+        if tuple(k_pool.shape[2:]) != (KV, DK) or tuple(v_pool.shape[2:]) != (KV, DV) or v_pool.shape[:2] != k_pool.shape[:2]:
+            raise KernelError("head_prep: the pools do not fit the heads")
+        pool_slots = k_pool.shape[0] * k_pool.shape[1]
+    channels = H * DK + (KV * DK if has_k else 0)
+    n_taps = 0
+    tail_stride = 0
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != channels:
+            raise KernelError("head_prep: one bias per query and key channel")
+    if taps is not None:
+        _need(taps, "taps", torch.float32)
+        n_taps = taps.shape[1]
+        if taps.shape[0] != channels:
+            raise KernelError("head_prep: one filter per query and key channel")
+        if n_taps > 1:
+            if tails is None or tails.dtype != torch.float32 or tails.stride(-1) != 1 or tails.shape[1] < channels * (n_taps - 1):
+                raise KernelError("head_prep: the filter needs fp32 tails of channels * (taps - 1) per slot")
+            tail_stride = tails.stride(0)
+    half = 0
+    if cos is not None:
+        _need(cos, "cos", torch.float32)
+        _need(sin, "sin", torch.float32)
+        half = cos.shape[1]
+        if cos.shape != (n, half) or sin.shape != (n, half):
+            raise KernelError("head_prep: angles must be [tokens, half]")
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _need(w, "norm weight", torch.float32)
+    q = torch.empty((n, H * DK), dtype=proj.dtype, device=proj.device)
+    _done(_lib().oxr_head_prep(q.data_ptr(), _ptr(k_pool) if has_k else None, _ptr(v_pool) if has_k else None, proj.data_ptr(), n, int(n_requests),
+                               proj.shape[1], int(q_col0), int(k_col0 or 0), int(v_col0 or 0), H, KV, DK, DV, int(has_k), v_mode, _ptr(bias), _ptr(taps),
+                               n_taps, _ptr(tails) if n_taps > 1 else None, tail_stride, HEAD_NORMS[norm], int(bool(norm_after_rotation)), _ptr(q_weight),
+                               _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), half, slots.data_ptr(), pool_slots, req_of_token.data_ptr(),
+                               cu_q.data_ptr(), state_slots.data_ptr(), _dtype_code(proj), status.data_ptr(), _stream()), "head_prep")
+    return q
+
+
+def sigmoid_gate_(o: torch.Tensor, proj: torch.Tensor, gate_col0: int, value_dim: int, per_head: bool) -> torch.Tensor:
+    """In place ``o[t, h * d + j] *= sigmoid(proj[t, gate_col0 + c])`` with ``c = h`` (``per_head``: one gate per head) or ``c = h * d + j`` (one per
+    channel); the sigmoid in fp32."""
+    _need(o, "o")
+    _need(proj, "proj", o.dtype)
+    n, inner = o.shape
+    cols = inner // value_dim if per_head else inner
+    if inner % value_dim or gate_col0 + cols > proj.shape[1]:
+        raise KernelError("sigmoid_gate: sizes do not fit")
+    _done(_lib().oxr_sigmoid_gate(o.data_ptr(), proj.data_ptr(), n, proj.shape[1], int(gate_col0), inner, int(value_dim), int(bool(per_head)),
+                                  _dtype_code(o), _stream()), "sigmoid_gate")
+    return o
+
+
+def gla_scan(proj: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, z: torch.Tensor, z_bias: torch.Tensor, *, heads: int, key_dim: int,
+             value_dim: int, tau: float, q_scale: float, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int) -> torch.Tensor:
+    """Gated linear attention over a packed step: per head ``S_t = diag(alpha_t) S_(t-1) + k_t v_t^T``, ``o_t = S_t^T (q_t * q_scale)`` with the decay
+    ``alpha_t = sigmoid(z_t + z_bias)^(1 / tau)`` per key channel. ``proj`` holds q, k and v head by head from the given columns; ``z [tokens, heads *
+    key_dim]`` is fp32; ``state`` (fp32, first axis the slot: S ``[heads, key_dim, value_dim]``) is read and left at the state after each request's
+    last token. Returns fp32 ``o [tokens, heads * value_dim]``."""
+    _need(proj, "proj")
+    _need(z, "z", torch.float32)
+    _need(z_bias, "z_bias", torch.float32)
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise KernelError("gla_scan: the state must be fp32 rows of heads x key_dim x value_dim")
+    n = proj.shape[0]
+    if z.shape != (n, heads * key_dim) or z_bias.numel() != heads * key_dim:
+        raise KernelError("gla_scan: the decay logits must be [tokens, heads * key_dim] with one bias each")
+    y = torch.empty((n, heads * value_dim), dtype=torch.float32, device=proj.device)
+    _done(_lib().oxr_gla_scan(y.data_ptr(), proj.data_ptr(), int(n_requests), proj.shape[1], int(q_col0), int(k_col0), int(v_col0), z.data_ptr(),
+                              z_bias.data_ptr(), float(tau), int(heads), int(key_dim), int(value_dim), float(q_scale), state.data_ptr(), state.stride(0),
+                              cu_q.data_ptr(), state_slots.data_ptr(), _dtype_code(proj), _stream()), "gla_scan")
+    return y
+
+
+def pair_norm_mean(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float) -> torch.Tensor:
+    """``0.5 * (rmsnorm(a) * wa + rmsnorm(b) * wb)`` row by row (fp32 arithmetic, rounded once to ``a.dtype``)."""
+    _need(a, "a")
+    _need(b, "b", a.dtype)
+    _need(wa, "wa", torch.float32)
+    _need(wb, "wb", torch.float32)
+    if a.shape != b.shape or wa.numel() != a.shape[1] or wb.numel() != a.shape[1]:
+        raise KernelError("pair_norm_mean: sizes do not fit")
+    out = torch.empty_like(a)
+    _done(_lib().oxr_pair_norm_mean(out.data_ptr(), a.data_ptr(), b.data_ptr(), wa.data_ptr(), wb.data_ptr(), a.shape[0], a.shape[1], float(eps),
+                                    _dtype_code(a), _stream()), "pair_norm_mean")
+    return out
+
+
+def tanh_cap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place ``x <- cap * tanh(x / cap)`` (fp32)."""
+    _need(x, "x", torch.float32)
+    _done(_lib().oxr_tanh_cap(x.data_ptr(), float(cap), x.numel(), _stream()), "tanh_cap")
+    return x
+
+
+def expert_silu_glu(gu: torch.Tensor, gate: torch.Tensor | None, ff: int, *, on_input: bool) -> torch.Tensor:
+    """The SiLU-gated unit over the stacked gate and up projections of all experts: ``gu [tokens, E * 2 ff]`` holds, expert by expert,
+    ``[gate (ff) | up (ff)]``. With the token's weight ``w = gate[t, e]`` (0: not chosen, the columns become 0; ``gate`` None: 1):
+    ``on_input``: ``silu(w g) * (w u)``, the weight on what the expert reads; else ``w * silu(g) * u``."""
+    _need(gu, "gu")
+    n, cols2 = gu.shape
+    E = cols2 // (2 * ff)
+    if cols2 != E * 2 * ff or E < 1:
+        raise KernelError("expert_silu_glu: sizes do not fit")
+    if gate is not None:
+        _need(gate, "gate", torch.float32)
+        if gate.shape != (n, E):
+            raise KernelError("expert_silu_glu: sizes do not fit")
+    a = torch.empty((n, E * ff), dtype=gu.dtype, device=gu.device)
+    _done(_lib().oxr_expert_silu_glu(a.data_ptr(), gu.data_ptr(), _ptr(gate), n, E, int(ff), int(bool(on_input)), _dtype_code(gu), _stream()),
+          "expert_silu_glu")
+    return a
+
+
+def scale_placed_rows_(x: torch.Tensor, place: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """In place ``x[place[p]] *= weights[p]`` for every (token, choice) pair p (``place`` as ``expert_sort`` returns it)."""
+    _need(x, "x")
+    _need(place, "place", torch.int32)
+    _need(weights, "weights", torch.float32)
+    if place.numel() != weights.numel():
+        raise KernelError("scale_placed_rows: one weight per pair")
+    _done(_lib().oxr_scale_placed_rows(x.data_ptr(), place.data_ptr(), weights.data_ptr(), place.numel(), x.shape[1], _dtype_code(x), _stream()),
+          "scale_placed_rows")
+    return x
+
+
+def add_row_gated_(y: torch.Tensor, s: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+    """In place ``y[t] += sigmoid(z[t]) * s[t]`` with one fp32 logit ``z[t]`` per row."""
+    _need(y, "y")
+    _need(s, "s", y.dtype)
+    _need(z, "z", torch.float32)
+    if s.shape != y.shape or z.numel() != y.shape[0]:
+        raise KernelError("add_row_gated: sizes do not fit")
+    _done(_lib().oxr_add_row_gated(y.data_ptr(), s.data_ptr(), z.data_ptr(), y.shape[0], y.shape[1], _dtype_code(y), _stream()), "add_row_gated")
+    return y

@@ -5,7 +5,8 @@ Two kinds of library: ``core`` (everything whose code does not depend on a model
 costs only what that model needs; ``build_all`` compiles a given list up front. Objects are compiled in
 parallel, a progress line goes to stderr every few seconds, and the result is kept beside the sources
 (``csrc/_build``) when that folder can be written, else in a per-user folder under the system's temp
-directory. A hash of the sources and flags decides whether a built library is still current.
+directory. A hash of the sources and flags decides whether a built library is still current, and a hash per
+source file whether its object of an earlier build can be linked again (``_build/objects``).
 
 There is no fallback: if nvcc is missing or a compile fails, :class:`BuildError` is raised.
 """
@@ -28,7 +29,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 CORE_SOURCES = ["elementwise.cu", "qk_norm_rope.cu", "gemm_f32.cu", "gemm_skinny.cu", "gemm_stream.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "gemm_tcgen05_few_rows.cu", "sampling.cu",
-                "stream_ops.cu", "mamba.cu", "attention_rows.cu", "attention_mix.cu", "attention_mix_mma.cu", "conv_qkv.cu", "mlstm.cu", "experts.cu"]
+                "stream_ops.cu", "mamba.cu", "attention_rows.cu", "attention_mix.cu", "attention_mix_mma.cu", "conv_qkv.cu", "mlstm.cu", "experts.cu", "head_prep.cu", "gla.cu"]
 ATTENTION_SOURCES = ["attention.cu"]
 HEADERS = ["common.cuh", "tma.cuh", "umma.cuh", "sampling_static.h"]
 
@@ -110,11 +111,18 @@ def _compile(lib_name: str, sources: list[str], defines: list[str]) -> Path:
             work = Path(tempfile.mkdtemp(prefix=f"{lib_name}_", dir=out_dir))
             try:
                 jobs = []
+                objects: list[Path] = []
+                kept = out_dir / "objects"      # objects of earlier builds, by the hash of their source, the headers and the flags
+                kept.mkdir(exist_ok=True)
                 for src in sources:
+                    cached = kept / f"{lib_name}_{Path(src).stem}_{_digest([src], defines)[:24]}.o"
+                    objects.append(cached)
+                    if cached.is_file():
+                        continue    # this file, the headers and the flags are those of an earlier build
                     obj = work / (Path(src).stem + ".o")
                     cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *defines, "-I", str(CSRC), "-c", str(CSRC / src), "-o", str(obj)]
                     log = open(work / (Path(src).stem + ".log"), "w+")
-                    jobs.append((src, obj, log, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT)))
+                    jobs.append((src, (obj, cached), log, subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT)))
                 last = time.monotonic()
                 while any(p.poll() is None for *_, p in jobs):
                     time.sleep(0.2)
@@ -131,8 +139,13 @@ def _compile(lib_name: str, sources: list[str], defines: list[str]) -> Path:
                         failed.append(f"--- {src} (exit {p.returncode}) ---\n{text}")
                 if failed:
                     raise BuildError("nvcc failed:\n" + "\n".join(failed))
+                for _, (obj, cached), _, _ in jobs:
+                    os.replace(obj, cached)
+                for old in kept.glob(f"{lib_name}_*.o"):      # objects of sources as they no longer are
+                    if old not in objects:
+                        old.unlink(missing_ok=True)
                 tmp_lib = work / lib.name
-                link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp_lib), *[str(o) for _, o, _, _ in jobs]]
+                link = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp_lib), *[str(o) for o in objects]]
                 res = subprocess.run(link, capture_output=True, text=True)
                 if res.returncode != 0:
                     raise BuildError(f"link of {lib.name} failed:\n{res.stdout}\n{res.stderr}")

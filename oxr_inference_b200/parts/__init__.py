@@ -1,6 +1,7 @@
 """Parts a decoder is assembled from; importing the package registers the built-in ones."""
 
-from oxr_inference_b200.parts import attention, block, experts, joint, masked_attention, mamba, mlp, mlstm, norm, rope  # noqa: F401  (register themselves)
+from oxr_inference_b200.parts import (attention, block, experts, gated_attention, gla, joint, masked_attention, mamba, mlp, mlstm, norm,  # noqa: F401
+                                      paired, rope)  # noqa: F401  (register themselves)
 from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, JOINTS, MIXERS, NORMS, POSITION_ENCODINGS,
                                            DeferredLinear, Embedding, FeedForward, GroupView, Head, Joint, LayerCache, Mixer, Norm, PagedKVNeed,
                                            ParamInfo, Part, PositionEncoding, Runtime, StateNeed, StepContext)

@@ -85,6 +85,8 @@ class PagedKVNeed:
     chunk: int = 0
     """> 0: a query sees only keys of its own chunk of that many positions (counted from 0); pages wholly before the chunk of the next
     query are released."""
+    keep_first: int = 0
+    """With a window: the request's first ``keep_first`` keys stay visible to every later query, so the pages that hold them are never released."""
 
     @property
     def v_dim(self) -> int:

@@ -112,6 +112,55 @@ class SandwichNormBlock:
         return None, stream
 
 
+@ARRANGEMENTS.register("output_norm")
+class OutputNormBlock:
+    """``x += norm1(mixer(x))`` and, when the block has a feed-forward, ``x += norm2(ff(x))``: the sublayers read the stream itself and the only
+    norms stand on their OUTPUTS. The fp32 stream is kept whole, as in ``sandwich_norm``: ``forward`` takes it in ``residual`` (the first block:
+    in ``x``), updates it in place and returns ``(None, stream)``. What a sublayer reads is the stream rounded to the activation dtype (in a
+    32-bit engine the stream itself); the norm of a sublayer's output, the add and that rounding for the next sublayer are one kernel. The
+    rounded stream a block ends with travels to the next block of this arrangement in the step's shared dictionary."""
+
+    supports_deferred = False
+    accepts_deferred_input = False
+    _KEY = "output_norm_rounded_stream"
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward | None, feed_forward_norm: Norm | None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward comes with its norm or not at all")
+        if not hasattr(mixer_norm, "add_normed"):
+            raise ValueError("the output_norm arrangement keeps the stream whole: its norms must offer add_normed")
+        self.mixer, self.mixer_norm, self.feed_forward, self.feed_forward_norm = mixer, mixer_norm, feed_forward, feed_forward_norm
+
+    def parts(self) -> dict[str, object]:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out.update(feed_forward=self.feed_forward, feed_forward_norm=self.feed_forward_norm)
+        return out
+
+    def forward(self, x, residual: torch.Tensor | None, ctx: StepContext, cache: LayerCache, defer_output: bool = False):
+        if residual is None:
+            if isinstance(x, DeferredLinear):
+                x = x.materialize()
+            if x.dtype != torch.float32:
+                raise ValueError("this arrangement keeps the stream in fp32: the embedding must hand it over whole")
+            stream = x
+        elif x is not None:
+            raise ValueError("this arrangement takes the stream whole; the block before it left an output that is not yet added")
+        else:
+            stream = residual
+        dtype = self.mixer_norm.runtime.dtype
+        whole = dtype == torch.float32           # a 32-bit engine's sublayers read the stream itself
+        kept = ctx.shared.pop(self._KEY, None)
+        h = stream if whole else (kept[1] if kept is not None and kept[0] is stream else ops.cast(stream, dtype))
+        a = self.mixer.forward(h, ctx, cache)
+        h = self.mixer_norm.add_normed(stream, a, rounded=not whole)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.add_normed(stream, self.feed_forward.forward(stream if whole else h), rounded=not whole)
+        if not whole:
+            ctx.shared[self._KEY] = (stream, h)
+        return None, stream
+
+
 @ARRANGEMENTS.register("parallel")
 class ParallelBlock(Part):
     """``x <- x + (mixer(h) + feed_forward(h))`` with ONE norm, ``h = norm(x)``, that both sublayers read (the feed-forward may be absent).

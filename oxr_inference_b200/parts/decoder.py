@@ -40,11 +40,16 @@ class TokenEmbedding(Embedding):
 @HEADS.register("linear_head")
 class OutputHead(Head):
     """``logits = h W^T`` in fp32 (oxr_runtime/language.py:158,213-214). ``tied``: W is the embedding table, which
-    the reference does not offer (its head is always a tensor of its own). ``scale``: the fp32 logits are multiplied by it."""
+    the reference does not offer (its head is always a tensor of its own). ``scale``: the fp32 logits are multiplied by it. ``softcap`` > 0:
+    the logits then become ``softcap * tanh(logits / softcap)``."""
 
-    def __init__(self, runtime: Runtime, embedding: Embedding, *, vocab_size: int, hidden_size: int, tied: bool, scale: float = 1.0):
+    def __init__(self, runtime: Runtime, embedding: Embedding, *, vocab_size: int, hidden_size: int, tied: bool, scale: float = 1.0,
+                 softcap: float = 0.0):
         self.runtime, self.embedding = runtime, embedding
         self.vocab, self.hidden, self.tied, self.scale = int(vocab_size), int(hidden_size), bool(tied), float(scale)
+        self.softcap = float(softcap)
+        if self.softcap < 0:
+            raise ValueError("softcap must not be negative (0 turns it off)")
         self.weight: torch.Tensor | None = None
 
     def parameters(self) -> dict[str, ParamInfo]:
@@ -59,7 +64,9 @@ class OutputHead(Head):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         w = self.embedding.weight if self.tied else self.weight
         logits = ops.linear(h, w, torch.float32)
-        return logits if self.scale == 1.0 else ops.scale_(logits, self.scale)
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
+        return ops.tanh_cap_(logits, self.softcap) if self.softcap > 0 else logits
 
 
 class DecoderModel:

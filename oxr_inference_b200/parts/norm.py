@@ -54,11 +54,11 @@ class RMSNorm(Norm):
     def stream_rows(self, stream: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         return ops.stream_rms_norm(stream, self.weight, self.eps, self.runtime.dtype, rows=rows)
 
-    def add_normed(self, stream: torch.Tensor, y: torch.Tensor, then: "RMSNorm | None" = None) -> torch.Tensor | None:
+    def add_normed(self, stream: torch.Tensor, y: torch.Tensor, then: "RMSNorm | None" = None, rounded: bool = False) -> torch.Tensor | None:
         """``stream += rmsnorm(y) * weight`` in place; with ``then`` (the next sublayer's pre-norm) also returns its output, from the
-        same pass over the row."""
+        same pass over the row; with ``rounded`` (and no ``then``) the new stream rounded to ``y``'s dtype."""
         if then is None:
-            return ops.norm_add_norm(stream, y, self.weight, self.eps)
+            return ops.norm_add_norm(stream, y, self.weight, self.eps, rounded=rounded)
         return ops.norm_add_norm(stream, y, self.weight, self.eps, then.weight, then.eps)
 
 
