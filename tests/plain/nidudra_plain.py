@@ -291,8 +291,12 @@ def forward(cfg: dict, w: dict, tokens: list[int], streams: list | None = None, 
     return logits
 
 
-def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> list[int]:
-    tokens = list(prompt)
+def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> tuple[list[int], list[float]]:
+    """``n`` greedy tokens after ``prompt`` and, for each, how far its logit stood above the runner-up's."""
+    tokens, gaps = list(prompt), []
     for _ in range(n):
-        tokens.append(int(forward(cfg, w, tokens)[-1].argmax()))
-    return tokens[len(prompt):]
+        last = forward(cfg, w, tokens)[-1]
+        best = torch.topk(last, 2).values
+        gaps.append(float(best[0] - best[1]))
+        tokens.append(int(last.argmax()))
+    return tokens[len(prompt):], gaps
