@@ -71,22 +71,27 @@ MODEL_B = model_config([paired(heads=2, kv_heads=1, dim=32, conv=2, rot=32, base
                         paired(heads=3, kv_heads=3, dim=48, conv=4, rot=0, r_heads=4, r_dim=70, r_vdim=33, tau=1.5, rank=9)],
                        width=64, vocab=200, eps=1e-6, softcap=5.0)
 # every attention layer has sizes that the tensor-core kernels take in bfloat16 (keys and values of one size, a multiple of 16)
-MODEL_C = model_config([windowed(heads=8, kv_heads=2, dim=64, vdim=64, size=33, keep_first=5, scale=0.2, mlp=moe(ff=32, experts=4, top=2, shared=16)),
+# and its only router stands in the last layer, where a choice that a rounding step turns over spoils one row and no later one
+MODEL_C = model_config([windowed(heads=8, kv_heads=2, dim=64, vdim=64, size=33, keep_first=5, scale=0.2, mlp=dense(ff=48)),
                         sinked(heads=6, kv_heads=3, dim=32, vdim=32, rot=32, base=500.0, scale=0.5, mlp=dense(ff=32)),
                         paired(heads=4, kv_heads=1, dim=128, conv=5, rot=64, base=1e3, scale=0.1, r_heads=2, r_dim=64, r_vdim=64, tau=8.0, rank=8),
                         windowed(heads=8, kv_heads=2, dim=64, vdim=64, size=100, keep_first=70, scale=0.2, kv_from=0, mlp=dense(ff=40)),
-                        windowed(heads=2, kv_heads=1, dim=48, vdim=48, size=17, keep_first=16, scale=0.25)],
+                        windowed(heads=2, kv_heads=1, dim=48, vdim=48, size=17, keep_first=16, scale=0.25, mlp=moe(ff=32, experts=4, top=2, shared=16))],
                        width=56, vocab=150, eps=1e-5, softcap=30.0)
 
 
-def make_folder(tmp: Path, config: dict, name: str, seed: int = 0, sharpen: float = 5.0) -> Path:
-    """A model folder with random bfloat16 weights, then reshaped so that faults show: the q/k norm weights (or, where the norm has none, the
-    projections) are scaled up for peaked attention (a lost, doubled or wrongly placed key changes the output), sinks get the size of the
-    scores, biases and filters a visible size, the decay's bias keeps the state alive over many tokens, the routers' scores are spread out,
-    the two sides' output weights differ."""
+def make_folder(tmp: Path, config: dict, name: str, seed: int = 0, sharpen: float = 2.0, strength: float = 1.0) -> Path:
+    """A model folder with random bfloat16 weights, then reshaped so that faults show: the q/k norm weights are scaled up for peaked attention
+    (a lost, doubled or wrongly placed key changes the output), sinks get the size of the scores, biases and filters a visible size, the
+    decay's bias keeps the state alive over many tokens, the routers' scores are spread out, gates and experts leave their linear stretch,
+    the two sides' output weights differ. ``strength`` < 1 scales all of that down towards plain random weights, for 16-bit runs of deep
+    models, where every factor here also multiplies what a rounding step does."""
     from safetensors.torch import load_file, save_file
 
     from oxr_inference_b200.weights import write_random_model
+
+    def by(factor: float) -> float:
+        return 1.0 + (factor - 1.0) * strength
 
     folder = write_random_model(config, tmp / name, seed, dtype="bfloat16", std=0.06)
     path = folder / "model.safetensors"
@@ -94,29 +99,29 @@ def make_folder(tmp: Path, config: dict, name: str, seed: int = 0, sharpen: floa
     for k, t in tensors.items():
         f = t.float()
         if k.endswith((".q.norm", ".k.norm")):
-            f = f * sharpen ** 0.5
+            f = f * by(sharpen) ** 0.5
         elif k.endswith(".mix.sink"):
             f = f * 30 + 1.0
         elif k.endswith((".q.b", ".k.b")):
-            f = f * 8
+            f = f * by(8)
         elif k.endswith(".conv"):
             f = f * 6 + 0.4
         elif k.endswith(".a2.b"):
             f = f * 10 + 2.5
         elif k.endswith((".a1", ".a2")):
-            f = f * 4
+            f = f * by(4)
         elif k.endswith("left.out"):
             f = f * 0.7
         elif k.endswith("right.out"):
             f = f * 1.4
         elif k.endswith((".router", ".shared.sg")):
-            f = f * 6
+            f = f * by(2)
         elif k.endswith((".gate", ".up")) and ".mlp." in k:
-            f = f * 4
+            f = f * by(4)
         elif k.endswith((".mix.g", ".right.g")):
-            f = f * 5
+            f = f * by(5)
         elif k.endswith(("head", "embed")):
-            f = f * 4
+            f = f * by(4)
         tensors[k] = f.to(t.dtype)
     save_file(tensors, str(path), metadata={"format": "pt"})
     (folder / "config.json").write_text(json.dumps(config, indent=1))
