@@ -806,6 +806,226 @@ def vazepel_workload(args) -> int:
     return 0
 
 
+def nidudra_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int, layers: int, vocab: int, experts: int = 16, top: int = 4) -> dict:
+    """A Nidudra model of a real model's layer sizes. Its layers take turns of four: windowed attention (the last 1,024 keys beside the first 64;
+    q/k norm, a gate per channel); causal attention with half of each head rotated (rescaled in bands), unit-norm q and k, a sink and a gate per
+    head; the pair (causal attention behind a filter of 4 taps with rescaled rotation, beside gated linear attention with ``width / 256`` heads
+    of 128 keys and 256 values); windowed attention again that reads the first layer's keys and values. All with the head sizes of the Qwen3
+    model beside it. The feed-forwards alternate between the gated layer of that model and experts (``top`` of ``experts``, each an eighth of
+    ``ff`` wide, with a shared expert of half of ``ff``: a token runs ``ff`` columns in all)."""
+    sizes = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top)}, "router": {"experts": experts, "top": top}, "shared": {"ff": ff // 2}}
+    out = []
+    for i in range(layers):
+        first = i // 4 * 4
+        windowed = {**sizes, "mask": {"size": 1024, "keep_first": 64}}
+        sinked = {**sizes, "rot": {"dims": head_dim // 2, "base": 50000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
+        pair = {"left": {**sizes, "conv": 4, "rot": {"dims": head_dim // 2, "base": 20000.0, "scaling": {"factor": 8.0, "original": 512, "fast": 32.0, "slow": 1.0}}},
+                "right": {"heads": max(width // 256, 1), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}}
+        kind, mixer = (("attention", windowed), ("attention_2", sinked), ("parallel", pair), ("attention", {**windowed, "kv_from": first}))[i % 4]
+        out.append({"type": kind, "mixer": mixer, "mlp": (dense, moe)[i % 2]})
+    return {"architecture": "Nidudra", "norm": {"eps": 1e-5}, "vocab": vocab, "width": width, "logit_softcap": 30.0, "layers": out}
+
+
+def nidudra_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: int) -> list[dict]:
+    """Each kernel of the design alone, at one model size, beside the like kernel of the paths that were there before: device time (median, L2
+    flushed between calls), the bytes or FLOPs it has to move or do, and the fraction of the measured peak."""
+    import torch
+
+    from oxr_inference_b200 import ops
+
+    dev = "cuda"
+    hbm_gbs, bf16_tflops, _ = peaks()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    status = ops.new_status(dev)
+    bf = torch.bfloat16
+    rows = []
+
+    def put(name, like, ms, *, bytes_=None, flops=None):
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            row.update(gb_s=round(bytes_ / (ms * 1e-3) / 1e9, 1), frac=round(bytes_ / (ms * 1e-3) / 1e9 / hbm_gbs, 4), bound="hbm")
+        else:
+            row.update(tflop_s=round(flops / (ms * 1e-3) / 1e12, 2), frac=round(flops / (ms * 1e-3) / 1e12 / bf16_tflops, 4), bound="tensor")
+        rows.append(row)
+
+    P, T, B, CTX = 16, 2048, 8, 2048
+    H, KV, D = heads, kv_heads, head_dim
+    WINDOW, KEEP, TAPS = 1024, 64, 4
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rand(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    n_pages = B * (CTX // P) + T // P + 8
+    k_pool, v_pool = rand(n_pages, P, KV, D), rand(n_pages, P, KV, D)
+    cq, ck, cv = H * D, KV * D, KV * D
+    ones = torch.ones(D, device=dev)
+    cos_table = torch.ones(8192, D // 2, device=dev)
+    maps = ops.make_kv_maps(k_pool.unsqueeze(0), v_pool.unsqueeze(0), P)
+    GH, GK, GV = max(width // 256, 1), 128, 256       # the recurrence's heads, keys and values
+    for name, q_lens, ctx_lens in (("prefill 2048", [T], [T]), ("decode b8", [1] * B, [CTX] * B)):
+        n, prefill = sum(q_lens), q_lens[0] > 1
+        R = len(q_lens)
+        cu = i32([0] + list(torch.tensor(q_lens).cumsum(0)))
+        req = torch.repeat_interleave(torch.arange(R, dtype=torch.int32), torch.tensor(q_lens)).to(dev)
+        pos = i32(list(range(T)) if prefill else [CTX - 1] * B)
+        slots = i32([(r * (CTX // P)) * P + (i if prefill else CTX - 1) for r, x in enumerate(q_lens) for i in range(x)])
+        table = torch.stack([torch.arange(r * (CTX // P), r * (CTX // P) + CTX // P + 1, dtype=torch.int32) % n_pages for r in range(R)]).to(dev).contiguous()
+        state_slots = i32(list(range(R)))
+        # ---- between the product and attention
+        qkv = rand(n, cq + ck + cv, scale=0.5)
+        ms = _time_ms(lambda: ops.qk_norm_rope_store(qkv, ones, ones, cos_table, cos_table, pos, slots, k_pool, v_pool, H, KV, D, 1e-6, status), flush=flush)
+        put(f"qk_norm_rope_store {name}", None, ms, bytes_=n * (cq + ck + cv) * 2 * 2)
+        cos = torch.ones(n, D // 4, device=dev)
+        common = dict(num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=D, k_pool=k_pool, v_pool=v_pool, slots=slots, req_of_token=req, cu_q=cu,
+                      state_slots=state_slots, n_requests=R, status=status, eps=1e-5)
+        ms = _time_ms(lambda: ops.head_prep(qkv, q_col0=0, k_col0=cq, v_col0=cq + ck, norm="weighted", q_weight=ones, k_weight=ones, **common), flush=flush)
+        put(f"head_prep {name} (weighted q/k norm, cache write)", f"qk_norm_rope_store {name}", ms, bytes_=n * (cq + ck + cv) * 2 * 2)
+        ms = _time_ms(lambda: ops.head_prep(qkv, q_col0=0, k_col0=cq, v_col0=cq + ck, norm="unit", norm_after_rotation=True, cos=cos, sin=cos, **common), flush=flush)
+        put(f"head_prep {name} (half of each head rotated, unit norm, cache write)", f"qk_norm_rope_store {name}", ms, bytes_=n * (cq + ck + cv) * 2 * 2)
+        qk = rand(n, cq + ck, scale=0.5)
+        bias, taps = rand(cq + ck, dtype=torch.float32), rand(cq + ck, TAPS, dtype=torch.float32)
+        tails = torch.zeros(R, (cq + ck) * (TAPS - 1), device=dev)
+        ms = _time_ms(lambda: ops.head_prep(qk, q_col0=0, k_col0=cq, v_col0=None, values_are_keys=True, bias=bias, taps=taps, tails=tails, norm="weighted",
+                                            q_weight=ones, k_weight=ones, cos=cos, sin=cos, **common), flush=flush)
+        put(f"head_prep {name} (biases, {TAPS} taps, values = keys, norm, rotation, cache write, tails)", f"qk_norm_rope_store {name}", ms,
+            bytes_=n * ((cq + ck) * 2 + (cq + ck + cv) * 2))
+        # ---- attention
+        def tiles_for(spec):
+            r_ = [r for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for _ in range(0, x, spec[0])]
+            t_ = [t0 for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for t0 in range(0, x, spec[0])]
+            return i32(r_ + [0]), i32(t_ + [0]), len(r_)
+        q3 = rand(n, H, D)
+        sink = torch.zeros(H, device=dev)
+        seen_causal = T * (T + 1) // 2 if prefill else sum(ctx_lens)
+        seen_window = sum(min(p_ + 1, WINDOW) + max(0, min(KEEP, p_ + 1 - WINDOW)) for p_ in (range(T) if prefill else [CTX - 1] * B))
+        for tma in (True, False):
+            specs = ops.attention_tile_specs(H, KV, D, bf, P if tma else None)
+            args = dict(tiles={spec: tiles_for(spec) for spec in specs}, cu_q=cu, ctx_lens=i32(ctx_lens), block_table=table, page_size=P, scale=D ** -0.5,
+                        kv_len_bound=max(ctx_lens), status=status)
+            kind = ("tcgen05, TMA" if prefill else "TMA split-KV") if tma else ("cp.async mma" if prefill else "cp.async split-KV")
+            ms = _time_ms(lambda: ops.paged_attention(q3, k_pool, v_pool, window=0, kv_maps=maps if tma else None, **args), flush=flush)
+            if prefill:
+                put(f"paged_attention {name} ({kind})", None, ms, flops=2 * 2 * H * D * seen_causal)
+            else:
+                put(f"paged_attention {name} ({kind})", None, ms, bytes_=seen_causal * KV * 2 * D * 2)
+            if not tma:
+                like = f"paged_attention {name} ({kind})"
+                ms = _time_ms(lambda: ops.paged_attention(q3, k_pool, v_pool, window=0, sink=sink, **args), flush=flush)
+                if prefill:
+                    put(f"sink attention {name} (causal, a sink per head; {kind})", like, ms, flops=2 * 2 * H * D * seen_causal)
+                else:
+                    put(f"sink attention {name} (causal, a sink per head; {kind})", like, ms, bytes_=seen_causal * KV * 2 * D * 2)
+                ms = _time_ms(lambda: ops.paged_attention(q3, k_pool, v_pool, window=WINDOW, keep_first=KEEP, **args), flush=flush)
+                if prefill:
+                    put(f"windowed attention {name} (last {WINDOW} keys beside the first {KEEP}; {kind})", like, ms, flops=2 * 2 * H * D * seen_window)
+                else:
+                    put(f"windowed attention {name} (last {WINDOW} keys beside the first {KEEP}; {kind})", like, ms, bytes_=seen_window * KV * 2 * D * 2)
+        o = rand(n, H * D)
+        gates = rand(n, H * D)
+        gates_pair = rand(n, 2 * H * D)
+        ms = _time_ms(lambda: ops.silu_mul(gates_pair), flush=flush)
+        put(f"silu_mul {name} ({H * D} columns)", None, ms, bytes_=n * H * D * 6)
+        ms = _time_ms(lambda: ops.sigmoid_gate_(o, gates, 0, D, per_head=False), flush=flush)
+        put(f"sigmoid_gate {name} (a gate per channel, in place)", f"silu_mul {name} ({H * D} columns)", ms, bytes_=n * H * D * 6)
+        # ---- the recurrences
+        inner, keys = GH * GV, GH * GK
+        gproj = rand(n, 2 * keys + 2 * inner, scale=0.3)
+        z, zb = torch.randn(n, keys, device=dev), torch.full((keys,), 3.0, device=dev)
+        gstate = torch.zeros(R + 1, GH * GK * GV, device=dev)
+        mgates, mbias = torch.randn(n, 2 * GH, device=dev), torch.zeros(2 * GH, device=dev)
+        mstate = torch.zeros(R + 1, GH * GK * GV + GH * GK + GH, device=dev)
+        ms = _time_ms(lambda: ops.mlstm_scan(gproj, 0, keys, 2 * keys, mgates, mbias, heads=GH, key_dim=GK, value_dim=GV, cap=15.0, q_scale=GK ** -0.5,
+                                             state=mstate, cu_q=cu, state_slots=state_slots, n_requests=R), flush=flush)
+        moved = n * (2 * keys + inner) * 2 + n * inner * 4 + R * GH * GK * GV * 4 * 2
+        put(f"mlstm_scan {name} ({GH} heads of {GK} x {GV})", None, ms, bytes_=moved)
+        ms = _time_ms(lambda: ops.gla_scan(gproj, 0, keys, 2 * keys, z, zb, heads=GH, key_dim=GK, value_dim=GV, tau=16.0, q_scale=GK ** -0.5, state=gstate,
+                                           cu_q=cu, state_slots=state_slots, n_requests=R), flush=flush)
+        put(f"gla_scan {name} ({GH} heads of {GK} x {GV}, a decay per key channel)", f"mlstm_scan {name} ({GH} heads of {GK} x {GV})", ms, bytes_=moved + n * keys * 4)
+        y, wn = torch.randn(n, inner, device=dev), torch.ones(inner, device=dev)
+        ms = _time_ms(lambda: ops.head_norm_gate(y, gproj, 2 * keys + inner, wn, GH, 1e-5), flush=flush)
+        put(f"head_norm_gate {name} (sigmoid gate)", None, ms, bytes_=n * inner * (4 + 2 + 2))
+        ms = _time_ms(lambda: ops.head_norm_gate(y, gproj, 2 * keys + inner, wn, GH, 1e-5, silu=True), flush=flush)
+        put(f"head_norm_gate {name} (SiLU gate)", f"head_norm_gate {name} (sigmoid gate)", ms, bytes_=n * inner * (4 + 2 + 2))
+        # ---- the stream
+        stream, w = torch.randn(n, width, device=dev), torch.ones(width, device=dev)
+        x, x2 = rand(n, width), rand(n, width)
+        ms = _time_ms(lambda: ops.add_rms_norm(x, stream, w, 1e-6), flush=flush)
+        put(f"add_rms_norm {name}", None, ms, bytes_=n * width * (2 + 4 + 4 + 2))
+        ms = _time_ms(lambda: ops.norm_add_norm(stream, x, w, 1e-5, rounded=True), flush=flush)
+        put(f"norm_add_norm {name} (norm of the output, add, rounded stream)", f"add_rms_norm {name}", ms, bytes_=n * width * (2 + 4 + 4 + 2))
+        ms = _time_ms(lambda: ops.pair_norm_mean(x, x2, w, w, 1e-5), flush=flush)
+        put(f"pair_norm_mean {name}", f"add_rms_norm {name}", ms, bytes_=n * width * (2 + 2 + 2))
+        # ---- experts' activation over all experts' columns
+        E, top, ffe = 16, 4, ff // 8
+        u = rand(n, E * ffe)
+        gate = torch.rand(n, E, device=dev)
+        ms = _time_ms(lambda: ops.gated_relu2(u, gate, ffe), flush=flush)
+        put(f"gated_relu2 {name} (all {E} experts' columns)", None, ms, bytes_=n * E * ffe * 4)
+        gu = rand(n, E * 2 * ffe)
+        ms = _time_ms(lambda: ops.expert_silu_glu(gu, gate, ffe, on_input=True), flush=flush)
+        put(f"expert_silu_glu {name} (all {E} experts' gate and up columns, weight on the input)", f"gated_relu2 {name} (all {E} experts' columns)", ms,
+            bytes_=n * E * ffe * 6)
+    # ---- the feed-forwards as a whole, beside the dense gated one
+    from oxr_inference_b200.parts.base import FEED_FORWARDS, Runtime
+
+    rt = Runtime(device=torch.device(dev), dtype=bf, max_positions=1, status=status)
+    E, top, ffe = 16, 4, ff // 8
+    gate_up_w, dense_down_w = rand(2 * ff, width, scale=0.02), rand(width, ff, scale=0.02)
+    moe = FEED_FORWARDS.build("routed_experts", rt, hidden_size=width, intermediate_size=ffe, experts=E, top=top, activation="silu_glu", score="sigmoid",
+                              renormalize=False, weight_on="input", shared={"kind": "swiglu", "params": {"hidden_size": width, "intermediate_size": ff // 2}},
+                              shared_gate=True)
+    for name, info in moe.parameters().items():
+        moe.assign(name, rand(*info.shape, scale=0.02))
+    moe.finish_loading()
+    for n in (T, B):
+        h = rand(n, width)
+        dense_name = f"dense gated feed-forward {n} rows (three products of {ff})"
+        ms = _time_ms(lambda: ops.linear(ops.silu_mul(ops.linear(h, gate_up_w)), dense_down_w), flush=flush)
+        weights_dense = 3 * ff * width * 2
+        put(dense_name, None, ms, **({"flops": 2 * n * width * 3 * ff} if n >= 256 else {"bytes_": weights_dense}))
+        ms = _time_ms(lambda: moe.forward(h), flush=flush)
+        touched = E * (1 - (1 - top / E) ** n)
+        put(f"routed SiLU experts {n} rows ({top} of {E} of {ffe}, gated shared {ff // 2})", dense_name, ms,
+            **({"flops": 2 * n * width * 3 * ff} if n >= 256 else {"bytes_": 3 * width * 2 * (touched * ffe + ff // 2)}))
+    ops.check_status(status)
+    return rows
+
+
+def nidudra_workload(args) -> int:
+    """The Nidudra design beside Qwen3 at equal sizes: whole-model prefill and decode throughput at two sizes, and every kernel of the new
+    parts against its roofline beside the like kernel of the paths that were there before."""
+    import torch
+
+    sizes = [("2048 wide, 8 layers", dict(width=2048, ff=8192, heads=16, kv_heads=4, head_dim=128, layers=8, vocab=32768)),
+             ("4096 wide, 8 layers (Qwen3-8B layer sizes)", dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=8, vocab=32768))]
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {"workload": "nidudra", "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)", "steps": K, "warmup": W,
+           "batch": 8, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks()[2], "sizes": []}
+    for name, s in sizes:
+        qwen = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": s["width"], "intermediate_size": s["ff"],
+                "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
+                "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": s["vocab"], "tie_word_embeddings": False,
+                "max_position_embeddings": 8192}
+        row = {"size": name}
+        for design, cfg in (("qwen3", qwen), ("nidudra", nidudra_config(**s))):
+            row[design] = design_throughput(cfg, s["vocab"], K, W, 8, args.context, PREFILL_TOKENS)
+            torch.cuda.empty_cache()
+        out["sizes"].append(row)
+    last = sizes[-1][1]
+    out["kernels"] = nidudra_kernels(last["width"], last["heads"], last["kv_heads"], last["head_dim"], last["ff"])
+    out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -816,9 +1036,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the further points (quick runs)")
     ap.add_argument("--skip-serving", action="store_true", help="leave the two serving workloads out of `points`")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
-    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel", "bifusun", "vazepel"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel", "bifusun", "vazepel", "nidudra"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each; "
-                         "radapel / bifusun / vazepel: that design beside Qwen3 at equal sizes, whole models and kernel by kernel")
+                         "radapel / bifusun / vazepel / nidudra: that design beside Qwen3 at equal sizes, whole models and kernel by kernel")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -831,6 +1051,8 @@ def main() -> int:
         return bifusun_workload(args)
     if args.workload == "vazepel":
         return vazepel_workload(args)
+    if args.workload == "nidudra":
+        return nidudra_workload(args)
     if args.workload != "decode":
         return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)

@@ -381,11 +381,43 @@ __global__ void expert_silu_glu_kernel(T* __restrict__ a, const T* __restrict__ 
     a[i] = Num<T>::from_f32(w == 0.f ? 0.f : out);
 }
 
+// The same for bf16 and expert widths that are whole 16-byte words: eight columns of one expert per thread.
+__global__ void expert_silu_glu_bf16x8_kernel(__nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ gu, const float* __restrict__ gate_w,
+                                              size_t words, int ff, int E, int on_input) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= words) return;
+    const int cols = E * ff, per_row = cols / 8;
+    const size_t t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8, e = c / ff, k = c - e * ff;
+    const float w = gate_w != nullptr ? gate_w[t * E + e] : 1.f;
+    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+        const __nv_bfloat16* src = gu + t * 2 * cols + (size_t)e * 2 * ff + k;
+        const uint4 gw = *reinterpret_cast<const uint4*>(src), uw = *reinterpret_cast<const uint4*>(src + ff);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gw);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uw);
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+        const float wi = on_input ? w : 1.f, wo = on_input ? 1.f : w;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            const float gx = g.x * wi, gy = g.y * wi;
+            o2[j] = __floats2bfloat162_rn(wo * (gx / (1.f + expf(-gx)) * (u.x * wi)), wo * (gy / (1.f + expf(-gy)) * (u.y * wi)));
+        }
+    }
+    *reinterpret_cast<uint4*>(a + t * cols + c) = packed;
+}
+
 OXR_API int oxr_expert_silu_glu(void* a, const void* gu, const float* gate_w, int n_tokens, int E, int ff, int on_input, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (E <= 0 || ff <= 0) return OXR_BAD_ARGUMENT;
     const size_t total = (size_t)n_tokens * E * ff;
     const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 1 && ff % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)gu % 16 == 0) {
+        const size_t words = total / 8;
+        expert_silu_glu_bf16x8_kernel<<<(unsigned)((words + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)gu, gate_w, words, ff, E, on_input);
+        return oxr_launch_status();
+    }
     if (dtype == 0) expert_silu_glu_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)gu, gate_w, total, ff, E, on_input);
     else expert_silu_glu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)gu, gate_w, total, ff, E, on_input);
     return oxr_launch_status();

@@ -590,10 +590,61 @@ __global__ void pair_norm_mean_kernel(T* __restrict__ out, const T* __restrict__
         out[at + i] = Num<T>::from_f32(0.5f * (Num<T>::to_f32(a[at + i]) * ia * wa[i] + Num<T>::to_f32(b[at + i]) * ib * wb[i]));
 }
 
+// The same for bf16 rows that are whole 16-byte words: a thread keeps its VPT words of both inputs in registers, so every row is read once.
+template <int VPT>
+__global__ void pair_norm_mean_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                             const float* __restrict__ wa, const float* __restrict__ wb, int hidden, float eps) {
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden / 8;
+    float av[VPT][8], bv[VPT][8];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int idx = threadIdx.x + v * blockDim.x;
+        if (idx < nvec) {
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(a + at + 8 * idx), av[v]);
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(b + at + 8 * idx), bv[v]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                sa = fmaf(av[v][i], av[v][i], sa);
+                sb = fmaf(bv[v][i], bv[v][i], sb);
+            }
+        }
+    }
+    sa = block_sum(sa, red);
+    sb = block_sum(sb, red);
+    const float ia = 0.5f / sqrtf(sa / (float)hidden + eps), ib = 0.5f / sqrtf(sb / (float)hidden + eps);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int idx = threadIdx.x + v * blockDim.x;
+        if (idx < nvec) {
+            const float4 a0 = *reinterpret_cast<const float4*>(wa + 8 * idx), a1 = *reinterpret_cast<const float4*>(wa + 8 * idx + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(wb + 8 * idx), b1 = *reinterpret_cast<const float4*>(wb + 8 * idx + 4);
+            const float wva[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, wvb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = av[v][i] * ia * wva[i] + bv[v][i] * ib * wvb[i];
+            *reinterpret_cast<uint4*>(out + at + 8 * idx) = f32_to_bf16x8(o);
+        }
+    }
+}
+
 OXR_API int oxr_pair_norm_mean(void* out, const void* a, const void* b, const float* wa, const float* wb, int n, int hidden, float eps, int dtype,
                                cudaStream_t stream_) {
     if (n <= 0) return 0;
     if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    if (dtype == 1 && hidden % 8 == 0 && hidden <= 32768 && (uintptr_t)out % 16 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)b % 16 == 0 &&
+        (uintptr_t)wa % 16 == 0 && (uintptr_t)wb % 16 == 0) {
+        const int nvec = hidden / 8;
+        const int vpt = nvec <= 512 ? 1 : (nvec <= 2048 ? 2 : 4);
+        const int threads_v = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+        const __nv_bfloat16 *ab = (const __nv_bfloat16*)a, *bb = (const __nv_bfloat16*)b;
+        if (vpt == 1) pair_norm_mean_bf16x8_kernel<1><<<n, threads_v, 0, stream_>>>((__nv_bfloat16*)out, ab, bb, wa, wb, hidden, eps);
+        else if (vpt == 2) pair_norm_mean_bf16x8_kernel<2><<<n, threads_v, 0, stream_>>>((__nv_bfloat16*)out, ab, bb, wa, wb, hidden, eps);
+        else pair_norm_mean_bf16x8_kernel<4><<<n, threads_v, 0, stream_>>>((__nv_bfloat16*)out, ab, bb, wa, wb, hidden, eps);
+        return oxr_launch_status();
+    }
     const int threads = hidden >= 2048 ? 256 : 128;
     if (dtype == 0) pair_norm_mean_kernel<float><<<n, threads, 0, stream_>>>((float*)out, (const float*)a, (const float*)b, wa, wb, hidden, eps);
     else pair_norm_mean_kernel<__nv_bfloat16><<<n, threads, 0, stream_>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb, hidden, eps);

@@ -473,7 +473,9 @@ def test_marked_keys_tiled_kernels(where, shape, sink):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,KV,DK,taps,half,norm,after,vmode", [(4, 2, 16, 3, 4, "weighted", False, "keys"), (3, 1, 24, 1, 12, "unit", True, "copy"),
                                                                 (2, 2, 40, 5, 0, None, False, "copy"), (5, 5, 8, 0, 3, "weighted", True, "keys"),
-                                                                (2, 1, 64, 2, 32, "unit", False, None)])
+                                                                (2, 1, 64, 2, 32, "unit", False, None), (4, 2, 128, 4, 32, "weighted", False, "keys"),
+                                                                (6, 2, 64, 3, 16, "unit", True, "copy"), (3, 3, 48, 0, 8, "weighted", True, "copy"),
+                                                                (5, 1, 256, 2, 128, "weighted", False, "keys"), (2, 2, 24, 3, 0, "unit", False, "keys")])
 def test_head_prep_against_the_formulas(dtype, H, KV, DK, taps, half, norm, after, vmode):
     """Two requests in unequal portions down to one token, fed step by step: bias, filter with its tails, the values that are the filtered
     keys, norm before or after the rotation, the rotation of pairs (i, i + half), the cache rows; against float64, token by token."""
@@ -636,13 +638,24 @@ def test_small_kernels_against_their_formulas(dtype):
         got = ops.add_row_gated_(yy.clone().to(DEV), s.to(DEV), z.to(DEV))
         near(got, yy.double() + torch.sigmoid(z.double())[:, None] * s.double(), "add_row_gated")
     # the sigmoid gate per channel and per head
+    for n, H, DV, lead in ((7, 3, 10, 4), (7, 3, 16, 8), (40, 5, 24, 16)):      # odd sizes, and rows of whole 16-byte words
+        o, proj = rnd(n, H * DV).to(dtype), rnd(n, lead + H * DV).to(dtype)
+        got = ops.sigmoid_gate_(o.clone().to(DEV), proj.to(DEV), lead, DV, per_head=False)
+        near(got, o.double() * torch.sigmoid(proj[:, lead:].double()), "gate per channel")
+        got = ops.sigmoid_gate_(o.clone().to(DEV), proj.to(DEV), 2, DV, per_head=True)
+        near(got, (o.double().reshape(n, H, DV) * torch.sigmoid(proj[:, 2:2 + H].double())[:, :, None]).reshape(n, -1), "gate per head")
     n, H, DV = 7, 3, 10
-    o, proj = rnd(n, H * DV).to(dtype), rnd(n, 4 + H * DV).to(dtype)
-    got = ops.sigmoid_gate_(o.clone().to(DEV), proj.to(DEV), 4, DV, per_head=False)
-    near(got, o.double() * torch.sigmoid(proj[:, 4:].double()), "gate per channel")
-    got = ops.sigmoid_gate_(o.clone().to(DEV), proj.to(DEV), 2, DV, per_head=True)
-    near(got, (o.double().reshape(n, H, DV) * torch.sigmoid(proj[:, 2:2 + H].double())[:, :, None]).reshape(n, -1), "gate per head")
     # SiLU-gated experts over stacked columns with the weight on the input, and on the output
+    for E, ff in ((4, 6), (3, 16)):
+        gu, gate = rnd(n, E * 2 * ff).to(dtype), torch.where(torch.rand(n, E, generator=g) < 0.5, torch.rand(n, E, generator=g), torch.zeros(n, E))
+        gud = gu.double().reshape(n, E, 2, ff)
+        wd = gate.double()[:, :, None]
+        got = ops.expert_silu_glu(gu.to(DEV), gate.to(DEV), ff, on_input=True)
+        near(got, (NP.silu(wd * gud[:, :, 0]) * (wd * gud[:, :, 1])).reshape(n, -1), "experts, weight on the input")
+        got = ops.expert_silu_glu(gu.to(DEV), gate.to(DEV), ff, on_input=False)
+        near(got, (wd * NP.silu(gud[:, :, 0]) * gud[:, :, 1]).reshape(n, -1), "experts, weight on the output")
+        got = ops.expert_silu_glu(gu.to(DEV), None, ff, on_input=True)
+        near(got, (NP.silu(gud[:, :, 0]) * gud[:, :, 1]).reshape(n, -1), "experts, no weight")
     E, ff = 4, 6
     gu, gate = rnd(n, E * 2 * ff).to(dtype), torch.where(torch.rand(n, E, generator=g) < 0.5, torch.rand(n, E, generator=g), torch.zeros(n, E))
     gud = gu.double().reshape(n, E, 2, ff)
