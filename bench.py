@@ -890,8 +890,9 @@ def nidudra_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         put(f"head_prep {name} (half of each head rotated, unit norm, cache write)", f"qk_norm_rope_store {name}", ms, bytes_=n * (cq + ck + cv) * 2 * 2)
         qk = rand(n, cq + ck, scale=0.5)
         bias, taps = rand(cq + ck, dtype=torch.float32), rand(cq + ck, TAPS, dtype=torch.float32)
+        taps_t = taps.t().contiguous()
         tails = torch.zeros(R, (cq + ck) * (TAPS - 1), device=dev)
-        ms = _time_ms(lambda: ops.head_prep(qk, q_col0=0, k_col0=cq, v_col0=None, values_are_keys=True, bias=bias, taps=taps, tails=tails, norm="weighted",
+        ms = _time_ms(lambda: ops.head_prep(qk, q_col0=0, k_col0=cq, v_col0=None, values_are_keys=True, bias=bias, taps=taps, taps_t=taps_t, tails=tails, norm="weighted",
                                             q_weight=ones, k_weight=ones, cos=cos, sin=cos, **common), flush=flush)
         put(f"head_prep {name} (biases, {TAPS} taps, values = keys, norm, rotation, cache write, tails)", f"qk_norm_rope_store {name}", ms,
             bytes_=n * ((cq + ck) * 2 + (cq + ck + cv) * 2))

@@ -10,7 +10,8 @@
 //   rotate : (a, b) = (y_i, y_(i + half)) -> (a cos - b sin, b cos + a sin) for i < half, angles per token; the rest passes
 //
 // Earlier tokens of the same request are read from the step's own rows, tokens before the step from the request's tail (fp32, the last
-// n - 1 projected values of every filtered channel, the most recent last); a second kernel moves the tails on after the step.
+// n - 1 projected values of every filtered channel, the oldest first, each a row of all channels); a second kernel moves the tails on
+// after the step.
 // Also here: the sigmoid gate on an attention output (per channel or per head), in place.
 #include "common.cuh"
 
@@ -21,9 +22,11 @@ struct PrepArgs {
     int has_k;               // 0: the mixer reads another layer's keys and values (queries only)
     int v_mode;              // 0: no values here; 1: the value projection is copied; 2: values are the filtered keys (DV == DK)
     const float* bias;       // [H DK + KV DK] for q then k, or null
-    const float* taps;       // [H DK + KV DK, n_taps] or null
+    const float* taps;       // [channels, n_taps] or null, channels = H DK + KV DK (H DK for a mixer without keys)
+    const float* taps_t;     // the same transposed, [n_taps, channels] (what the 16-byte kernel reads), or null
     int n_taps;
-    float* tails;            // [slots, (H DK + KV DK) * (n_taps - 1)], row stride tail_stride
+    int channels;
+    float* tails;            // [slots, (n_taps - 1) * channels]: entry (j, c) is channel c's projected value n_taps - 1 - j tokens back; row stride tail_stride
     long long tail_stride;
     int norm;                // 0 none, 1 with weight, 2 without
     int norm_after;          // the norm comes after the rotation
@@ -81,7 +84,7 @@ __global__ void __launch_bounds__(128) head_prep_kernel(T* __restrict__ q_out, T
             for (int back = a.n_taps - 1; back >= 0; --back) {       // oldest first: the order of the sum does not depend on the cut
                 float u;
                 if (back <= s) u = Num<T>::to_f32(proj[(size_t)(t - back) * a.stride + col0 + d]) + b;
-                else u = tail[(size_t)c * (a.n_taps - 1) + (a.n_taps - 1) - (back - s)];
+                else u = tail[(size_t)((a.n_taps - 1) - (back - s)) * a.channels + c];
                 v = fmaf(w[a.n_taps - 1 - back], u, v);
             }
         }
@@ -143,8 +146,12 @@ __device__ __forceinline__ void prep_load8(const float* p, float (&out)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
     out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
 }
-// sum of v over the `lph` lanes of this lane's head (lanes g0 .. g0 + lph - 1), in lane order; every lane of the warp calls it
+// sum of v over the `lph` lanes of this lane's head (lanes g0 .. g0 + lph - 1), in a fixed order; every lane of the warp calls it
 __device__ __forceinline__ float prep_head_sum(float v, int g0, int lph) {
+    if ((lph & (lph - 1)) == 0) {      // a power of two: the head's lanes are an aligned group, a butterfly stays inside it
+        for (int o = lph >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+    }
     float total = 0.f;
     for (int j = 0; j < lph; ++j) total += __shfl_sync(0xffffffffu, v, (g0 + j) & 31);
     return total;
@@ -191,8 +198,8 @@ __global__ void __launch_bounds__(128) head_prep_bf16x8_kernel(__nv_bfloat16* __
             for (int i = 0; i < 8; ++i) y[i] += b[i];
         } else {
             const int r = a.req_of_token[t], s = t - a.cu_q[r], keep = a.n_taps - 1;
-            const float* tail = keep > 0 ? a.tails + (long long)a.state_slots[r] * a.tail_stride + (size_t)c0 * keep : nullptr;
-            const float* w = a.taps + (size_t)c0 * a.n_taps;
+            const float* tail = keep > 0 ? a.tails + (long long)a.state_slots[r] * a.tail_stride + c0 : nullptr;
+            const float* w = a.taps_t + c0;
             for (int back = keep; back >= 0; --back) {       // oldest first: the order of the sum does not depend on the cut
                 float u[8];
                 if (back <= s) {
@@ -200,11 +207,12 @@ __global__ void __launch_bounds__(128) head_prep_bf16x8_kernel(__nv_bfloat16* __
 #pragma unroll
                     for (int i = 0; i < 8; ++i) u[i] += b[i];
                 } else {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) u[i] = tail[i * keep + keep - (back - s)];
+                    prep_load8(tail + (size_t)(keep - (back - s)) * a.channels, u);
                 }
+                float wj[8];
+                prep_load8(w + (size_t)(keep - back) * a.channels, wj);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[i] = fmaf(w[i * a.n_taps + keep - back], u[i], y[i]);
+                for (int i = 0; i < 8; ++i) y[i] = fmaf(wj[i], u[i], y[i]);
             }
         }
         if (!is_q && a.v_mode == 2)    // the values are the keys as they leave the filter
@@ -268,17 +276,17 @@ __global__ void prep_tail_kernel(const T* __restrict__ proj, const PrepArgs a, i
     const int q_ch = a.H * a.DK;
     const int col = c < q_ch ? a.q_col0 + c : a.k_col0 + (c - q_ch);
     const float b = a.bias != nullptr ? a.bias[c] : 0.f;
-    float* tail = a.tails + (long long)a.state_slots[r] * a.tail_stride + (size_t)c * keep;
+    float* tail = a.tails + (long long)a.state_slots[r] * a.tail_stride + c;
     float old[16];
-    for (int j = 0; j < keep; ++j) old[j] = tail[j];
+    for (int j = 0; j < keep; ++j) old[j] = tail[(size_t)j * channels];
     for (int j = 0; j < keep; ++j) {
-        const int back = keep - j;                 // tail[j] holds the value `back` tokens before the next one
-        tail[j] = back <= n ? Num<T>::to_f32(proj[(size_t)(t0 + n - back) * a.stride + col]) + b : old[j + n];
+        const int back = keep - j;                 // entry j holds the value `back` tokens before the next one
+        tail[(size_t)j * channels] = back <= n ? Num<T>::to_f32(proj[(size_t)(t0 + n - back) * a.stride + col]) + b : old[j + n];
     }
 }
 
 OXR_API int oxr_head_prep(void* q_out, void* k_pool, void* v_pool, const void* proj, int n_tokens, int n_requests, int stride, int q_col0, int k_col0,
-                          int v_col0, int H, int KV, int DK, int DV, int has_k, int v_mode, const float* bias, const float* taps, int n_taps, float* tails,
+                          int v_col0, int H, int KV, int DK, int DV, int has_k, int v_mode, const float* bias, const float* taps, const float* taps_t, int n_taps, float* tails,
                           long long tail_stride, int norm, int norm_after, const float* q_weight, const float* k_weight, float eps, const float* cos_t,
                           const float* sin_t, int half, const int* slots, long long pool_slots, const int* req_of_token, const int* cu_q,
                           const int* state_slots, int dtype, int* status, cudaStream_t stream) {
@@ -288,7 +296,7 @@ OXR_API int oxr_head_prep(void* q_out, void* k_pool, void* v_pool, const void* p
         return OXR_BAD_ARGUMENT;
     PrepArgs a;
     a.stride = stride; a.q_col0 = q_col0; a.k_col0 = k_col0; a.v_col0 = v_col0; a.H = H; a.KV = KV; a.DK = DK; a.DV = DV; a.has_k = has_k;
-    a.v_mode = has_k ? v_mode : 0; a.bias = bias; a.taps = taps; a.n_taps = taps != nullptr ? n_taps : 0; a.tails = tails; a.tail_stride = tail_stride;
+    a.v_mode = has_k ? v_mode : 0; a.bias = bias; a.taps = taps; a.taps_t = taps_t; a.n_taps = taps != nullptr ? n_taps : 0; a.channels = H * DK + (has_k ? KV * DK : 0); a.tails = tails; a.tail_stride = tail_stride;
     a.norm = norm; a.norm_after = norm_after; a.q_weight = q_weight; a.k_weight = k_weight; a.eps = eps; a.cos_t = half > 0 ? cos_t : nullptr;
     a.sin_t = sin_t; a.half = half; a.slots = slots; a.pool_slots = pool_slots; a.req_of_token = req_of_token; a.cu_q = cu_q;
     a.state_slots = state_slots; a.status = status;
@@ -301,7 +309,8 @@ OXR_API int oxr_head_prep(void* q_out, void* k_pool, void* v_pool, const void* p
     const bool words = dtype == 1 && DK % 8 == 0 && DV % 8 == 0 && DK <= 256 && (v_mode != 1 || DV <= DK) && half % 8 == 0 && stride % 8 == 0 && q_col0 % 8 == 0 &&
                        k_col0 % 8 == 0 && v_col0 % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)k_pool % 16 == 0 &&
                        (uintptr_t)v_pool % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)q_weight % 16 == 0 && (uintptr_t)k_weight % 16 == 0 &&
-                       (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0;
+                       (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0 &&
+                       (taps == nullptr || (taps_t != nullptr && (uintptr_t)taps_t % 16 == 0 && (n_taps < 2 || ((uintptr_t)tails % 16 == 0 && tail_stride % 4 == 0))));
     if (words) {
         const int lph = DK / 8, hpw = 32 / lph;
         const int per_block = 4 * hpw;
@@ -312,7 +321,7 @@ OXR_API int oxr_head_prep(void* q_out, void* k_pool, void* v_pool, const void* p
     else head_prep_kernel<__nv_bfloat16><<<grid, 32 * warps, smem, stream>>>((__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
                                                                             (const __nv_bfloat16*)proj, a);
     if (a.taps != nullptr && a.n_taps > 1) {
-        const int channels = H * DK + (has_k ? KV * DK : 0);
+        const int channels = a.channels;
         const int total = n_requests * channels;
         if (dtype == 0) prep_tail_kernel<float><<<(total + 127) / 128, 128, 0, stream>>>((const float*)proj, a, channels, n_requests);
         else prep_tail_kernel<__nv_bfloat16><<<(total + 127) / 128, 128, 0, stream>>>((const __nv_bfloat16*)proj, a, channels, n_requests);

@@ -162,7 +162,7 @@ def _lib():
         lib.oxr_attention_mix_mma_smem.argtypes = [i, i, i, i, i, i]
         lib.oxr_attention_mix_mma_smem.restype = c_longlong
         lib.oxr_expert_clamped_glu.argtypes = [p, p, p, i, i, i, f, f, i, p]
-        lib.oxr_head_prep.argtypes = [p, p, p, p, i, i, i, i, i, i, i, i, i, i, i, i, p, p, i, p, ll, i, i, p, p, f, p, p, i, p, ll, p, p, p, i, p, p]
+        lib.oxr_head_prep.argtypes = [p, p, p, p, i, i, i, i, i, i, i, i, i, i, i, i, p, p, p, i, p, ll, i, i, p, p, f, p, p, i, p, ll, p, p, p, i, p, p]
         lib.oxr_sigmoid_gate.argtypes = [p, p, i, i, i, i, i, i, i, p]
         lib.oxr_gla_scan.argtypes = [p, p, i, i, i, i, i, p, p, f, i, i, i, f, p, ll, p, p, i, p]
         lib.oxr_pair_norm_mean.argtypes = [p, p, p, p, p, i, i, f, i, p]
@@ -1763,14 +1763,14 @@ HEAD_NORMS = {None: 0, "weighted": 1, "unit": 2}
 
 def head_prep(proj: torch.Tensor, *, q_col0: int, k_col0: int | None, v_col0: int | None, values_are_keys: bool = False, num_heads: int,
               num_kv_heads: int, key_dim: int, value_dim: int, bias: torch.Tensor | None = None, taps: torch.Tensor | None = None,
-              tails: torch.Tensor | None = None, norm: str | None = None, norm_after_rotation: bool = False, q_weight: torch.Tensor | None = None,
+              taps_t: torch.Tensor | None = None, tails: torch.Tensor | None = None, norm: str | None = None, norm_after_rotation: bool = False, q_weight: torch.Tensor | None = None,
               k_weight: torch.Tensor | None = None, eps: float = 0.0, cos: torch.Tensor | None = None, sin: torch.Tensor | None = None,
               k_pool: torch.Tensor | None = None, v_pool: torch.Tensor | None = None, slots: torch.Tensor, req_of_token: torch.Tensor,
               cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int, status: torch.Tensor) -> torch.Tensor:
     """Query and key heads on their way from the projections ``proj [tokens, *]`` to attention, and the cache write. In this order, each step
     optional: ``bias [H DK + KV DK]`` (fp32, q then k) is added; every channel passes a causal filter ``taps [channels, n]`` (the last tap on
-    the current token; earlier tokens come from the step's rows or from the request's row of ``tails``, fp32 ``[slots, channels * (n - 1)]``,
-    which is moved on afterwards); with ``values_are_keys`` the filtered keys are stored as the values; every head is RMS-normed
+    the current token; ``taps_t``, the same transposed, lets the 16-byte bfloat16 kernel run; earlier tokens come from the step's rows or from
+    the request's row of ``tails``, fp32 ``[slots, (n - 1) * channels]``, the oldest value of all channels first, which is moved on afterwards); with ``values_are_keys`` the filtered keys are stored as the values; every head is RMS-normed
     (``norm="weighted"``: times ``q_weight`` / ``k_weight [DK]``; ``"unit"``: no weight) before or after the rotation; the pairs
     ``(i, i + half)`` of each head's first ``2 half`` entries turn by the token's angles (``cos``, ``sin`` fp32 ``[tokens, half]``). Keys and
     values go to ``k_pool`` / ``v_pool [pages, page_size, KV, D]`` at ``slots`` (-1: not stored); ``k_col0`` None: queries only. Returns
@@ -1799,6 +1799,10 @@ def head_prep(proj: torch.Tensor, *, q_col0: int, k_col0: int | None, v_col0: in
         n_taps = taps.shape[1]
         if taps.shape[0] != channels:
             raise KernelError("head_prep: one filter per query and key channel")
+        if taps_t is not None:
+            _need(taps_t, "taps_t", torch.float32)
+            if taps_t.shape != (n_taps, channels):
+                raise KernelError("head_prep: taps_t must be taps transposed")
         if n_taps > 1:
             if tails is None or tails.dtype != torch.float32 or tails.stride(-1) != 1 or tails.shape[1] < channels * (n_taps - 1):
                 raise KernelError("head_prep: the filter needs fp32 tails of channels * (taps - 1) per slot")
@@ -1816,7 +1820,7 @@ def head_prep(proj: torch.Tensor, *, q_col0: int, k_col0: int | None, v_col0: in
     q = torch.empty((n, H * DK), dtype=proj.dtype, device=proj.device)
     _done(_lib().oxr_head_prep(q.data_ptr(), _ptr(k_pool) if has_k else None, _ptr(v_pool) if has_k else None, proj.data_ptr(), n, int(n_requests),
                                proj.shape[1], int(q_col0), int(k_col0 or 0), int(v_col0 or 0), H, KV, DK, DV, int(has_k), v_mode, _ptr(bias), _ptr(taps),
-                               n_taps, _ptr(tails) if n_taps > 1 else None, tail_stride, HEAD_NORMS[norm], int(bool(norm_after_rotation)), _ptr(q_weight),
+                               _ptr(taps_t) if taps is not None else None, n_taps, _ptr(tails) if n_taps > 1 else None, tail_stride, HEAD_NORMS[norm], int(bool(norm_after_rotation)), _ptr(q_weight),
                                _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), half, slots.data_ptr(), pool_slots, req_of_token.data_ptr(),
                                cu_q.data_ptr(), state_slots.data_ptr(), _dtype_code(proj), status.data_ptr(), _stream()), "head_prep")
     return q

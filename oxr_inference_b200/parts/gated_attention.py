@@ -78,6 +78,7 @@ class GatedAttention(Mixer):
         self.vectors: dict[str, torch.Tensor] = {}
         self.bias: torch.Tensor | None = None
         self.conv: torch.Tensor | None = None
+        self.conv_t: torch.Tensor | None = None
 
     def _vector_shapes(self) -> dict[str, tuple[int, ...]]:
         out: dict[str, tuple[int, ...]] = {}
@@ -115,6 +116,7 @@ class GatedAttention(Mixer):
             self.bias = torch.cat([v[f"{n}.b"] for n in sides]).contiguous()
         if self.taps > 0:
             self.conv = torch.cat([v[f"{n}.conv"] for n in sides]).contiguous()
+            self.conv_t = self.conv.t().contiguous()      # [taps, channels]: what the 16-byte kernel reads
 
     # ---- what the mixer keeps
     def cache_need(self):
@@ -156,7 +158,7 @@ class GatedAttention(Mixer):
         v = self.vectors
         q = ops.head_prep(proj, q_col0=0, k_col0=self.cq if self.ck else None, v_col0=self.cq + self.ck if self.cv else None,
                           values_are_keys=self.values_are_keys, num_heads=self.H, num_kv_heads=self.KV, key_dim=self.DK, value_dim=self.DV,
-                          bias=self.bias, taps=self.conv, tails=cache.state, norm=self.qk_norm, norm_after_rotation=self.norm_after,
+                          bias=self.bias, taps=self.conv, taps_t=self.conv_t, tails=cache.state, norm=self.qk_norm, norm_after_rotation=self.norm_after,
                           q_weight=v.get("q.norm"), k_weight=v.get("k.norm"), eps=self.eps, cos=cos, sin=sin, k_pool=k_pool, v_pool=v_pool,
                           slots=group.slots if cache.store else ctx.no_store_slots, req_of_token=ctx.req_of_token, cu_q=ctx.cu_q,
                           state_slots=ctx.state_slots, n_requests=ctx.n_requests, status=ctx.status)

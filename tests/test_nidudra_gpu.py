@@ -514,7 +514,7 @@ def test_head_prep_against_the_formulas(dtype, H, KV, DK, taps, half, norm, afte
     P = 4
     k_pool = torch.zeros(12, P, KV, DK, dtype=dtype, device=DEV)
     v_pool = torch.zeros(12, P, KV, DV, dtype=dtype, device=DEV)
-    tails = torch.zeros(3, 7 + ch * max(taps - 1, 0), device=DEV)[:, 7:] if taps > 1 else None     # a view with a row stride of its own
+    tails = torch.zeros(3, 8 + ch * max(taps - 1, 0), device=DEV)[:, 8:] if taps > 1 else None     # a view with a row stride of its own
     status = ops.new_status(DEV)
     slot_of = [[(1 + 2 * r + 6 * (j // P // 2 * 0) + (j // P)) * P + j % P for j in range(n)] for r, n in enumerate(lens)]
     slot_of = [[((r * 5 + j // P) + 1) * P + j % P for j in range(n)] for r, n in enumerate(lens)]
@@ -536,7 +536,7 @@ def test_head_prep_against_the_formulas(dtype, H, KV, DK, taps, half, norm, afte
             cos, sin = ang.cos().float().to(DEV), ang.sin().float().to(DEV)
         q = ops.head_prep(torch.cat(rows).to(DEV), q_col0=0, k_col0=cq if has_k else None, v_col0=ch if vmode == "copy" else None,
                           values_are_keys=vmode == "keys", num_heads=H, num_kv_heads=KV, key_dim=DK, value_dim=DV, bias=None if bias is None else bias.to(DEV),
-                          taps=None if filt is None else filt.to(DEV), tails=tails, norm=norm, norm_after_rotation=after, q_weight=qw.to(DEV), k_weight=kw.to(DEV),
+                          taps=None if filt is None else filt.to(DEV), taps_t=None if filt is None else filt.t().contiguous().to(DEV), tails=tails, norm=norm, norm_after_rotation=after, q_weight=qw.to(DEV), k_weight=kw.to(DEV),
                           eps=eps, cos=cos, sin=sin, k_pool=k_pool if has_k else None, v_pool=v_pool if has_k else None, slots=i32(slots), req_of_token=i32(req_of),
                           cu_q=i32(cu), state_slots=i32([r + 1 for r in live]), n_requests=len(live), status=status)
         row = 0
@@ -558,7 +558,7 @@ def test_head_prep_against_the_formulas(dtype, H, KV, DK, taps, half, norm, afte
             assert (gv - want_v).abs().max() < tol * (1 + want_v.abs().max()), f"values of request {r}"
         if taps > 1:
             u = proj_all[r][:, :ch].double() + bias.double()
-            want_tail = u[n - (taps - 1):].T.reshape(-1)
+            want_tail = u[n - (taps - 1):].reshape(-1)      # the oldest value of every channel first
             assert (tails[r + 1].double().cpu() - want_tail).abs().max() < 1e-5 * (1 + want_tail.abs().max()), f"tails of request {r}"
     if taps > 1:
         assert tails[0].abs().max() == 0, "a slot nobody used was written"
