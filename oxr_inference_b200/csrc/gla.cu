@@ -10,20 +10,21 @@
 // not depend on how a prompt was cut into steps. Columns of S (one value dimension each) are independent: a block takes 32 columns of one
 // head of one request.
 //
-// grid (ceil(DV / 32), heads, requests); block = 32 * NW threads with NW = ceil(DK / 32). Lane l owns the value column p = 32 blockIdx.x + l,
-// warp w the key entries 32 w .. 32 w + 31: a thread keeps 32 entries of S in registers. A tile of TT tokens goes through shared memory at
+// grid (ceil(DV / 32), heads, requests); block = 32 * NW threads with NW = ceil(DK / KPT). Lane l owns the value column p = 32 blockIdx.x + l,
+// warp w the key entries KPT w .. KPT w + KPT - 1: a thread keeps KPT = 32 or 16 entries of S in registers (16: twice the warps for the same
+// state, which is what hides the loop's latencies when a step brings many tokens of a request; keys of up to 128). A tile of TT tokens goes through shared memory at
 // a time (thread d brings entry d of k, q and the decay of each token; the next tile's loads are in flight while this one is computed); the
 // warps' partial sums of S^T q meet in shared memory and are added in the order of the warps after the tile.
 #include "common.cuh"
 
 __device__ __forceinline__ float gla_log_sigmoid(float v) { return fminf(v, 0.f) - log1pf(expf(-fabsf(v))); }
 
-template <typename T, int NW, int TT>
+template <typename T, int NW, int TT, int KPT>
 __global__ void __launch_bounds__(32 * NW) gla_scan_kernel(
     float* __restrict__ y, const T* __restrict__ proj, int proj_stride, int q_col0, int k_col0, int v_col0, const float* __restrict__ z,
     const float* __restrict__ z_bias, float inv_tau, int heads, int DK, int DV, float q_scale, float* __restrict__ state, long long slot_stride,
     const int* __restrict__ cu_q, const int* __restrict__ state_slots) {
-    constexpr int KPT = 32, DKP = KPT * NW, NT = 32 * NW;
+    constexpr int DKP = KPT * NW, NT = 32 * NW;      // NT >= DKP: thread d brings key entry d of every token
     __shared__ __align__(16) float ks[TT][DKP];
     __shared__ __align__(16) float qs[TT][DKP];
     __shared__ __align__(16) float as[TT][DKP];
@@ -62,9 +63,11 @@ __global__ void __launch_bounds__(32 * NW) gla_scan_kernel(
     auto stash = [&]() {
 #pragma unroll
         for (int t = 0; t < TT; ++t) {
-            ks[t][n] = Num<T>::to_f32(kreg[t]);
-            qs[t][n] = Num<T>::to_f32(qreg[t]) * q_scale;
-            as[t][n] = expf(gla_log_sigmoid(zreg[t] + zb) * inv_tau);
+            if (n < DKP) {
+                ks[t][n] = Num<T>::to_f32(kreg[t]);
+                qs[t][n] = Num<T>::to_f32(qreg[t]) * q_scale;
+                as[t][n] = expf(gla_log_sigmoid(zreg[t] + zb) * inv_tau);
+            }
         }
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -122,14 +125,20 @@ __global__ void __launch_bounds__(32 * NW) gla_scan_kernel(
 
 OXR_API int oxr_gla_scan(float* y, const void* proj, int n_requests, int proj_stride, int q_col0, int k_col0, int v_col0, const float* z,
                          const float* z_bias, float tau, int heads, int DK, int DV, float q_scale, float* state, long long slot_stride, const int* cu_q,
-                         const int* state_slots, int dtype, cudaStream_t stream) {
+                         const int* state_slots, int dtype, int key_entries_per_thread, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (heads <= 0 || DK <= 0 || DK > 256 || DV <= 0 || heads > 65535 || n_requests > 65535 || !(tau > 0.f)) return OXR_BAD_ARGUMENT;
     dim3 grid((DV + 31) / 32, heads, n_requests);
-    const int nw = (DK + 31) / 32;
+    // 16 key entries a thread (twice the warps per head) where that still fits a block of 8 warps; key_entries_per_thread 16 or 32 forces one
+    const bool narrow = key_entries_per_thread == 16 ? DK <= 128 : (key_entries_per_thread == 32 ? false : DK <= 128);
+    const int nw = narrow ? (DK + 15) / 16 : (DK + 31) / 32;
 #define OXR_GLA(T, NW) \
-    gla_scan_kernel<T, NW, 8><<<grid, 32 * NW, 0, stream>>>(y, (const T*)proj, proj_stride, q_col0, k_col0, v_col0, z, z_bias, 1.f / tau, heads, DK, DV, \
-                                                           q_scale, state, slot_stride, cu_q, state_slots)
+    do { \
+        if (narrow) gla_scan_kernel<T, NW, 8, 16><<<grid, 32 * NW, 0, stream>>>(y, (const T*)proj, proj_stride, q_col0, k_col0, v_col0, z, z_bias, 1.f / tau, \
+                                                                                heads, DK, DV, q_scale, state, slot_stride, cu_q, state_slots); \
+        else gla_scan_kernel<T, NW, 8, 32><<<grid, 32 * NW, 0, stream>>>(y, (const T*)proj, proj_stride, q_col0, k_col0, v_col0, z, z_bias, 1.f / tau, heads, \
+                                                                         DK, DV, q_scale, state, slot_stride, cu_q, state_slots); \
+    } while (0)
 #define OXR_GLA_T(T) \
     do { \
         if (nw <= 1) OXR_GLA(T, 1); \

@@ -125,10 +125,11 @@ def test_one_mechanism(name, dtype, tmp_path):
     close(run_cut(r, ids, [2, 3, 2, 11, 2, 17, 1, 2, 21]), want, dtype, f"{name}, portions", mg)
 
 
-def test_experts_grouped_by_expert_equal_the_two_products_form(tmp_path):
+@pytest.mark.parametrize("width,ff,experts,top", [(64, 16, 6, 2), (40, 20, 5, 1), (72, 36, 3, 2), (48, 9, 4, 3)])
+def test_experts_grouped_by_expert_equal_the_two_products_form(width, ff, experts, top, tmp_path):
     """From ``grouped_min_rows`` tokens on every expert multiplies only the rows that chose it (their inputs scaled by the score first); below, all
-    experts are two products. Both against the plain sum, in both dtypes."""
-    cfg = NU.model_config([S(heads=1, kv_heads=1, dim=16, vdim=16, mlp=MOE(experts=6, top=2, ff=16, shared=24))], width=64)
+    experts are two products. Both against the plain sum, in both dtypes, also for widths that are no multiples of 16."""
+    cfg = NU.model_config([S(heads=1, kv_heads=1, dim=16, vdim=16, mlp=MOE(experts=experts, top=top, ff=ff, shared=24))], width=width)
     folder = NU.make_folder(tmp_path, cfg, "grouped", seed=8)
     ids = NU.tokens(cfg, 70, seed=3)
     want, mg = NU.plain_logits(folder, ids), NU.router_margins(folder, ids)
@@ -565,10 +566,11 @@ def test_head_prep_against_the_formulas(dtype, H, KV, DK, taps, half, norm, afte
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,DK,DV,tau", [(3, 12, 20, 4.0), (1, 70, 33, 1.5), (2, 64, 64, 16.0), (2, 130, 8, 40.0)])
-def test_gated_linear_attention_scan_continues_from_its_state(dtype, H, DK, DV, tau):
+@pytest.mark.parametrize("per_thread", [0, 16, 32])
+@pytest.mark.parametrize("H,DK,DV,tau", [(3, 12, 20, 4.0), (1, 70, 33, 1.5), (2, 64, 64, 16.0), (2, 130, 8, 40.0), (2, 128, 40, 8.0)])
+def test_gated_linear_attention_scan_continues_from_its_state(dtype, H, DK, DV, tau, per_thread):
     """Two requests in unequal portions over three steps against the recurrence in float64, token by token; the state a step leaves is the
-    state the next one starts from; a slot nobody uses stays zero."""
+    state the next one starts from; a slot nobody uses stays zero. With both splits of a head's key channels over threads."""
     from oxr_inference_b200 import ops
 
     g = torch.Generator().manual_seed(H + DK + DV)
@@ -590,7 +592,7 @@ def test_gated_linear_attention_scan_continues_from_its_state(dtype, H, DK, DV, 
             zs.append(inputs[r][1][at[r]:at[r] + cut[r]])
             cu.append(cu[-1] + cut[r])
         y = ops.gla_scan(torch.cat(projs).to(DEV), 0, H * DK, 2 * H * DK, torch.cat(zs).to(DEV), zb.to(DEV), heads=H, key_dim=DK, value_dim=DV, tau=tau,
-                         q_scale=DK ** -0.5, state=state, cu_q=i32(cu), state_slots=i32([2, 0]), n_requests=2)
+                         q_scale=DK ** -0.5, state=state, cu_q=i32(cu), state_slots=i32([2, 0]), n_requests=2, key_entries_per_thread=per_thread)
         for r in (0, 1):
             got[r].append(y[cu[r]:cu[r + 1]].cpu())
             at[r] += cut[r]
