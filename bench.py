@@ -820,12 +820,12 @@ def nidudra_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int
     for i in range(layers):
         first = i // 4 * 4
         windowed = {**sizes, "mask": {"size": 1024, "keep_first": 64}}
-        sinked = {**sizes, "rot": {"dims": head_dim // 2, "base": 50000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 1024}}}
-        pair = {"left": {**sizes, "conv": 4, "rot": {"dims": head_dim // 2, "base": 20000.0, "scaling": {"factor": 8.0, "original": 512, "fast": 32.0, "slow": 1.0}}},
-                "right": {"heads": max(width // 256, 1), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}}
+        sinked = {**sizes, "rot": {"dims": head_dim // 2, "base": 100000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 2048}}}
+        pair = {"left": {**sizes, "conv": 4, "rot": {"dims": head_dim // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 16.0, "slow": 2.0}}},
+                "right": {"heads": max(width // 256, 1), "dim": 128, "vdim": 256, "tau": 8.0, "rank": 64}}
         kind, mixer = (("attention", windowed), ("attention_2", sinked), ("parallel", pair), ("attention", {**windowed, "kv_from": first}))[i % 4]
         out.append({"type": kind, "mixer": mixer, "mlp": (dense, moe)[i % 2]})
-    return {"architecture": "Nidudra", "norm": {"eps": 1e-5}, "vocab": vocab, "width": width, "logit_softcap": 30.0, "layers": out}
+    return {"architecture": "Nidudra", "norm": {"eps": 1e-6}, "vocab": vocab, "width": width, "logit_softcap": 50.0, "layers": out}
 
 
 def nidudra_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: int) -> list[dict]:

@@ -144,10 +144,10 @@ def test_banded_frequencies_by_hand():
 
     # wavelengths 2 pi / f against original / high = 16 and original / low = 64
     f = [1.0, 2 * math.pi / 32.0, 2 * math.pi / 64.5, 0.01]
-    got = banded_frequencies(f, factor=8.0, low=1.0, high=4.0, original=64)
+    got = banded_frequencies(f, factor=6.0, low=1.0, high=4.0, original=64)
     s = (64 / 32.0 - 1.0) / 3.0
-    assert got[0] == 1.0 and got[3] == 0.01 / 8.0 and got[2] == f[2] / 8.0
-    assert abs(got[1] - ((1 - s) * f[1] / 8.0 + s * f[1])) < 1e-15
+    assert got[0] == 1.0 and got[3] == 0.01 / 6.0 and got[2] == f[2] / 6.0
+    assert abs(got[1] - ((1 - s) * f[1] / 6.0 + s * f[1])) < 1e-15
 
 
 def test_ramped_frequencies_by_hand():
