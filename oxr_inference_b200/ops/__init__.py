@@ -1823,6 +1823,8 @@ def head_prep(proj: torch.Tensor, *, q_col0: int, k_col0: int | None, v_col0: in
                                _ptr(taps_t) if taps is not None else None, n_taps, _ptr(tails) if n_taps > 1 else None, tail_stride, HEAD_NORMS[norm], int(bool(norm_after_rotation)), _ptr(q_weight),
                                _ptr(k_weight), float(eps), _ptr(cos), _ptr(sin), half, slots.data_ptr(), pool_slots, req_of_token.data_ptr(),
                                cu_q.data_ptr(), state_slots.data_ptr(), _dtype_code(proj), status.data_ptr(), _stream()), "head_prep")
+    global launch_count
+    launch_count += 1 if n_taps > 1 else 0      # the kernel that moves the tails on
     return q
 
 
